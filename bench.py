@@ -1,0 +1,201 @@
+"""Headline benchmark: the tensor-parallel MLP block made of the two fused GEMM + collective ops
+the baseline names — all_gather_matmul (A shard [M/ws, 8192], B [8192, 28672/ws]) followed by
+gemm_reduce_scatter (A [M, 28672/ws], B [28672/ws, 8192]) at M = 8192, bf16, synthetic data,
+random-initialised weights. One "step" = both ops back to back on one stream.
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --gpus N ...            # the unmodified reference (baseline/_ref)
+
+For N > 1 launch with torchrun (one rank per GPU); RANK / LOCAL_RANK / WORLD_SIZE / MASTER_* are
+read from the environment. Rank 0 prints ONE JSON line. `value` is the whole-job dense bf16
+throughput in TFLOP/s (sum over all ranks of 2*M*N*K per GEMM divided by the step time, device-timed
+with CUDA events, max over ranks); total work is fixed as N grows (strong scaling). Per-op
+microseconds, NVLink bytes and roofline fractions are in `ops`. Between timed iterations nothing is
+flushed: the step's working set (weights + activations, > 280 MB per rank at every N) exceeds the
+126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOKENS = 8192
+HIDDEN = 8192
+FFN = 28672
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", 0)),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    except Exception:
+        return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def _event_times(fn, steps, sync):
+    import torch
+
+    begins = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    sync()
+    for i in range(steps):
+        begins[i].record()
+        fn()
+        ends[i].record()
+    sync()
+    return [b.elapsed_time(e) for b, e in zip(begins, ends)]
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import kraken_b200
+    from kraken_b200 import fused
+    from kraken_b200.parallel import symm_mem
+    from kraken_b200.utils import ClockSampler, init_from_env
+
+    rank, local_rank, ws = init_from_env()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    M, H, F = M_TOKENS, HIDDEN, FFN
+    assert F % ws == 0 and M % ws == 0
+    Fl, Ml = F // ws, M // ws
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    # weights K-major (nn.Linear layout): w_up_t [F/ws, H], w_down_t [H, F/ws]
+    w_up_t = (0.02 * torch.randn(Fl, H, generator=g)).to(torch.bfloat16).to(dev)
+    w_down_t = (0.02 * torch.randn(H, Fl, generator=g)).to(torch.bfloat16).to(dev)
+    x_host = torch.randn(Ml, H, generator=g).to(torch.bfloat16).pin_memory()
+    x_symm = symm_mem.empty(Ml, H, dtype=torch.bfloat16, device=dev)
+    symm_mem.rendezvous(x_symm)
+    x_symm.copy_(x_host)
+    a_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    progress = torch.zeros(ws, dtype=torch.uint32, device=dev)
+    result_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def sync():
+        if ws > 1:
+            dist.barrier(device_ids=[dev.index])
+        torch.cuda.synchronize()
+
+    def step():
+        _, h = fused.all_gather_matmul(x_symm, w_up_t.t(), a_out=a_out, progress=progress)
+        return fused.gemm_reduce_scatter(h, w_down_t.t())
+
+    def step_e2e():
+        x_symm.copy_(x_host, non_blocking=True)          # H2D of this step's input (pinned)
+        y = step()
+        result_host.copy_(y.float().abs().mean().reshape(1), non_blocking=True)   # D2H of the step's metric
+        torch.cuda.current_stream().synchronize()
+
+    def op_ag():
+        fused.all_gather_matmul(x_symm, w_up_t.t(), a_out=a_out, progress=progress)
+
+    h_fixed = (torch.randn(M, Fl, generator=g).to(torch.bfloat16)).to(dev)
+
+    def op_rs():
+        fused.gemm_reduce_scatter(h_fixed, w_down_t.t())
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync()
+    kraken_b200.check_status()
+
+    sampler = ClockSampler(gpu_index=dev.index).start() if rank == 0 else None
+    t0 = time.perf_counter()
+    times = _event_times(step, args.steps, sync)
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop() if sampler is not None else None
+    kraken_b200.check_status()
+
+    def maxr(v):
+        if ws == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_step = maxr(sum(times) / len(times))
+    # per-op numbers (median, max over ranks)
+    ops = {}
+    for name, fn in (("all_gather_matmul", op_ag), ("gemm_reduce_scatter", op_rs)):
+        for _ in range(3):
+            fn()
+        ts = sorted(_event_times(fn, max(3, args.steps), sync))
+        ops[name] = {"us": maxr(ts[len(ts) // 2] * 1000.0)}
+    # end to end through the public API, with the H2D input copy and the D2H result read every step
+    for _ in range(3):
+        step_e2e()
+    sync()
+    t_e2e0 = time.perf_counter()
+    e2e_times = _event_times(step_e2e, args.steps, sync)
+    ms_e2e = maxr(sum(e2e_times) / len(e2e_times))
+    kraken_b200.check_status()
+
+    flops_step = 2.0 * M * F * H * 2          # whole job: two GEMMs of 2*M*(F)*(H) each
+    peaks = _peaks()
+    value = flops_step / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_step / (ms_e2e * 1e-3) / 1e12
+    per_gemm_flops_rank = 2.0 * M * F * H / ws
+    link = 770e9
+    for name, nv_bytes in (("all_gather_matmul", (ws - 1) * Ml * H * 2), ("gemm_reduce_scatter", (ws - 1) * Ml * H * 2)):
+        t_mma = per_gemm_flops_rank / (peaks["bf16_tflops"] * 1e12)
+        t_link = nv_bytes / link
+        roof = max(t_mma, t_link)
+        ops[name].update({"nvlink_bytes": nv_bytes, "roofline_us": roof * 1e6,
+                          "frac_of_roofline": roof * 1e6 / ops[name]["us"],
+                          "tflops_per_gpu": per_gemm_flops_rank / (ops[name]["us"] * 1e-6) / 1e12})
+    if rank == 0:
+        out = {
+            "metric": "tp_mlp_fused_ag_matmul_plus_gemm_rs_tflops",
+            "value": value, "unit": "TFLOP/s (bf16 dense, whole job)", "n_gpus": ws, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random activations, random-init weights)",
+            "impl": "kraken_b200",
+            "config": {"model": "tp_mlp_block(all_gather_matmul -> gemm_reduce_scatter)", "global_batch": M,
+                       "seq_len": 1, "hidden": H, "ffn": F, "parallelism": f"tp{ws}",
+                       "l2": "no flush: per-step working set exceeds the 126 MB L2",
+                       "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks"},
+            "ops": ops,
+            "roofline_denominators": peaks,
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s (bf16 dense, whole job)", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": Ml * H * 2, "d2h_bytes_per_step": 4},
+            "gpu_launches": 2 * args.steps,
+            "wall_s": wall,
+        }
+        print(json.dumps(out), flush=True)
+    if ws > 1:
+        dist.barrier(device_ids=[dev.index])
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline import reference_arm
+
+    reference_arm.main(args, M_TOKENS, HIDDEN, FFN)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,336 @@
+// Persistent, warp-specialised tcgen05 GEMM core shared by the plain GEMM and by the fused
+// all-gather->GEMM, GEMM->reduce-scatter and GEMM->all-reduce kernels.
+//
+//   D[128 x BN] tile = R[128 rows, K] * C[BN rows, K]^T      (both operands K-major, bf16)
+//
+// R ("row operand") and C ("column operand") are any two K-major matrices described by TMA
+// tensor maps; the host decides which of the user's A / B^T plays which role (for decode-sized
+// M the weights are the row operand and the epilogue stores the tile transposed).
+//
+// Warp roles in a 192-thread CTA (one CTA per SM):
+//   warp 0     TMA producer: fills a ring of shared-memory stages (128-byte swizzle)
+//   warp 1     allocates TMEM, one elected lane issues tcgen05.mma into one of two accumulators
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator, convert, stage through shared
+//              memory and write coalesced rows to local or PEER memory, while warp 1 already
+//              runs the next tile's main loop into the other accumulator.
+// The reference's main loops are tl.dot recipes (kraken/fused/all_gather_matmul.py:25-123,
+// kraken/fused/gemm_reduce_scatter_ce_persistent.py:46-134,
+// kraken/fused/gemm_one_shot_all_reduce_fused.py:10-103); nothing of their structure is reused.
+#pragma once
+#include "kraken/tcgen05.cuh"
+#include "kraken/vec.cuh"
+
+namespace kraken {
+
+constexpr int kGemmThreads = 192;
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kEpiWarpBytes = 8192;             // per-epilogue-warp staging: 32 rows x 256 B
+constexpr int kSmemLimit = 232448;              // 227 KB
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = kBM * kBK * 2;
+  static constexpr int B_BYTES = BN * kBK * 2;
+  static constexpr int B_BYTES_AL = (B_BYTES + 1023) / 1024 * 1024;
+  static constexpr int STAGE = A_BYTES + B_BYTES_AL;
+  static constexpr int EPI = 4 * kEpiWarpBytes;
+  static constexpr int RAW_STAGES = (kSmemLimit - 1024 /*align*/ - EPI - 512 /*barriers*/) / STAGE;
+  static constexpr int STAGES = RAW_STAGES > 8 ? 8 : RAW_STAGES;
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int SMEM = 1024 + STAGES * STAGE + EPI + 512;
+};
+
+enum GemmMode : int { GEMM_PLAIN = 0, GEMM_AG = 1, GEMM_RS = 2, GEMM_AR = 3, GEMM_CE = 4 };
+
+struct alignas(64) GemmParams {
+  CUtensorMap tmap_r;        // row operand, dims {K, rows_r}, box {64, 128}
+  CUtensorMap tmap_c;        // column operand, dims {K, rows_c}, box {64, BN}
+  CUtensorMap tmap_r_local;  // AG: this rank's own shard (read without waiting)
+  // problem
+  int rows_r, rows_c, K;
+  int tiles_r, tiles_c;      // tile counts
+  int group_r;               // consecutive row-tiles sharing column sweeps (L2 reuse)
+  int pivot_r;               // row-tile rotation (rank pivot)
+  int mode;
+  int transposed;            // 1: D tile is C^T (store element (i,j) at out[j][i])
+  int out_fp32;              // 1: fp32 output, 0: bf16
+  int num_mma_ctas;          // CTAs [0, num_mma_ctas) run the GEMM; the rest are comm CTAs (AG)
+  // output (PLAIN / AG / final result of RS and AR)
+  void* out;
+  long long ldo;             // elements between consecutive output rows
+  int out_rows, out_cols;    // bounds of `out` in the orientation it is stored
+  // collectives
+  int rank, ws;
+  void* const* bufs;         // [ws] symmetric workspaces (RS/AR staging, AG shards)
+  uint32_t* const* pads;     // [ws] signal pads
+  uint32_t pad_base;         // first barrier slot
+  uint32_t flag_base;        // first tile-flag word in the signal pad (RS / AR)
+  // AG
+  void* a_out;               // gathered A [ws * shard_rows, K]
+  uint32_t* progress;        // [ws * splits] chunk flags
+  uint32_t* counters;        // [ws * splits] arrival counters (zeroed, self-resetting)
+  int splits, shard_rows, chunk_rows;
+  // RS
+  int slab_rows;             // M / ws
+  SyncCtx sync;
+};
+
+// Linear persistent tile index -> (row tile, column tile): row tiles advance in groups of
+// `group_r` so that concurrently running CTAs share operand tiles in L2, then the row index is
+// rotated by `pivot_r` (rank pivot of the fused kernels).
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tr, int& tc) {
+  const int per_group = p.group_r * p.tiles_c;
+  const int g = t / per_group;
+  const int first = g * p.group_r;
+  const int gsz = min(p.tiles_r - first, p.group_r);
+  const int in = t - g * per_group;
+  tr = first + in % gsz;
+  tc = in / gsz;
+  tr += p.pivot_r;
+  if (tr >= p.tiles_r) tr -= p.tiles_r;
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Hooks a fused kernel supplies to the main loop.
+//   Producer hook: called by the producer lane before loading row tile `tr`; returns the tensor
+//   map to read it from and may rewrite the row coordinate; false aborts.
+//   Epilogue hook: decides where tile (tr, tc) is stored and what happens once it is stored.
+struct TileDest {
+  char* base;        // address of element (0,0) of the destination matrix
+  long long ld;      // elements per destination row
+  int row0, col0;    // where the tile's (0,0) lands in the destination
+  int rows, cols;    // destination bounds
+};
+
+template <int BN, class Hooks>
+__device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid, unsigned nb, Hooks& hooks,
+                                              unsigned char* smem_raw) {
+  using Cfg = GemmCfg<BN>;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  // ---- shared memory carve-up (1024-byte aligned for the 128-byte swizzle)
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t stage0 = smem_base;
+  unsigned char* epi_ptr = smem_al + Cfg::STAGES * Cfg::STAGE;
+  const uint32_t bars = smem_base + Cfg::STAGES * Cfg::STAGE + Cfg::EPI;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + 2 + a); };
+  uint32_t* tmem_slot = (uint32_t*)(smem_al + Cfg::STAGES * Cfg::STAGE + Cfg::EPI + 8 * (2 * Cfg::STAGES + 4));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.tiles_r * p.tiles_c;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (elect_one()) {
+      tma_prefetch_desc(&p.tmap_r);
+      tma_prefetch_desc(&p.tmap_c);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = bid; t < total_tiles && ok; t += nb) {
+        int tr, tc;
+        tile_coords(p, t, tr, tc);
+        const CUtensorMap* rmap = &p.tmap_r;
+        int row0 = tr * kBM;
+        ok = hooks.before_load(p, tr, rmap, row0);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, p.sync, 40);
+          if (!ok) break;
+          mbar_expect_tx(full_bar(s), Cfg::A_BYTES + Cfg::B_BYTES);
+          const uint32_t sa = stage0 + s * Cfg::STAGE;
+          tma_load_2d(sa, rmap, full_bar(s), kb * kBK, row0);
+          tma_load_2d(sa + Cfg::A_BYTES, &p.tmap_c, full_bar(s), kb * kBK, tc * BN);
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = bid; t < total_tiles && ok; t += nb, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+        ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, p.sync, 41);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full_bar(s), ph, p.sync, 42);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = stage0 + s * Cfg::STAGE;
+          const uint64_t adesc = make_smem_desc_sw128(sa);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit(tfull_bar(acc));   // accumulator complete
+      }
+    }
+  } else {
+    // ================= epilogue warps =================
+    const int q = warp & 3;                                  // TMEM lane quarter this warp may read
+    unsigned char* stg = epi_ptr + (warp - 2) * kEpiWarpBytes;
+    int it = 0;
+    bool ok = true;
+    for (int t = bid; t < total_tiles && ok; t += nb, ++it) {
+      int tr, tc;
+      tile_coords(p, t, tr, tc);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+      ok = mbar_wait(tfull_bar(acc), acc_ph, p.sync, 43);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      TileDest dst = hooks.tile_dest(p, tr, tc);
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+      if (p.transposed) {
+        // D(i, j) -> dst[col0 + j][row0 + i]: lanes = consecutive destination columns.
+        const int dcol = dst.row0 + q * 32 + lane;     // destination column index (tile row i)
+        constexpr int CH = BN < 32 ? BN : 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CH) {
+          uint32_t r[32];
+          if (CH == 32) tmem_ld32(t_addr + c0, r);
+          else tmem_ld16(t_addr + c0, r);
+          tmem_ld_wait();
+          if (c0 + CH >= BN) {
+            // all TMEM reads of this accumulator are done: hand it back before the global stores
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+          }
+          if (dcol < dst.cols) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int drow = dst.col0 + c0 + j;
+              if (drow < dst.rows) {
+                if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
+                else ((__nv_bfloat16*)dst.base)[(long long)drow * dst.ld + dcol] = __float2bfloat16(__uint_as_float(r[j]));
+              }
+            }
+          }
+        }
+      } else {
+        // Row-major store through per-warp staging: 32 rows x 256 bytes, 16-byte units XOR-swizzled
+        // by row so that both the row-per-lane writes and the row-contiguous reads are conflict-free.
+        const int elt = p.out_fp32 ? 4 : 2;
+        const int cols_per_pass = 256 / elt;               // 128 bf16 or 64 fp32 columns
+        const int passes = (BN + cols_per_pass - 1) / cols_per_pass;
+        const int pass_cols = BN < cols_per_pass ? BN : cols_per_pass;
+        const int units_per_row = pass_cols * elt / 16;    // 16-byte units actually used per row
+        const bool vec_ok = ((dst.ld * elt) % 16 == 0) && ((((uintptr_t)dst.base) & 15) == 0) && ((dst.col0 * elt) % 16 == 0);
+        for (int ps = 0; ps < passes; ++ps) {
+          constexpr int CH = BN < 32 ? BN : 32;
+          const int nch = pass_cols / CH;
+          for (int c = 0; c < nch; ++c) {
+            uint32_t r[32];
+            const int col = ps * cols_per_pass + c * CH;
+            if (CH == 32) tmem_ld32(t_addr + col, r);
+            else tmem_ld16(t_addr + col, r);
+            tmem_ld_wait();
+            if (ps == passes - 1 && c == nch - 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(acc));
+            }
+            if (p.out_fp32) {
+#pragma unroll
+              for (int u = 0; u < CH / 4; ++u) {
+                const int unit = c * (CH / 4) + u;
+                const int phys = (unit & 8) | ((unit ^ lane) & 7);
+                *(U4*)(stg + lane * 256 + phys * 16) = U4{r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]};
+              }
+            } else {
+#pragma unroll
+              for (int u = 0; u < CH / 8; ++u) {
+                const int unit = c * (CH / 8) + u;
+                const int phys = (unit & 8) | ((unit ^ lane) & 7);
+                U4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+                v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+                v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+                v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+                *(U4*)(stg + lane * 256 + phys * 16) = v;
+              }
+            }
+          }
+          __syncwarp();
+          // coalesced write-out: `rpi` rows per warp instruction
+          const int rpi = 32 / units_per_row > 0 ? 32 / units_per_row : 1;
+          const int unit = lane % units_per_row;
+          const int rsub = lane / units_per_row;
+          const int per_unit = 16 / elt;
+          const int gcol = dst.col0 + ps * cols_per_pass + unit * per_unit;
+          if (rsub < rpi) {
+            for (int r0 = 0; r0 < 32; r0 += rpi) {
+              const int rr = r0 + rsub;
+              const int grow = dst.row0 + q * 32 + rr;
+              const int phys = (unit & 8) | ((unit ^ rr) & 7);
+              const U4 v = *(const U4*)(stg + rr * 256 + phys * 16);
+              if (grow < dst.rows) {
+                char* gp = dst.base + ((long long)grow * dst.ld + gcol) * elt;
+                if (vec_ok && gcol + per_unit <= dst.cols) {
+                  st16(gp, v);
+                } else {
+                  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                  for (int e = 0; e < per_unit; ++e)
+                    if (gcol + e < dst.cols) {
+                      if (p.out_fp32) ((uint32_t*)gp)[e] = w[e];
+                      else ((uint16_t*)gp)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                    }
+                }
+              }
+            }
+          }
+          __syncwarp();
+        }
+      }
+      ok = hooks.after_store(p, tr, tc, q, lane);
+    }
+  }
+
+  // ---- teardown: every role arrives here, on the normal path and after a failed wait
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace kraken

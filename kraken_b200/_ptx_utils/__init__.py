@@ -1,0 +1,83 @@
+"""Synchronisation primitives.
+
+In the reference these are ``@triton.jit`` device functions (kraken/_ptx_utils/__init__.py:1-19:
+``symm_mem_sync``, ``send_signal``, ``get_flat_tid``, ``arrive_gmem_barrier``, ``wait_gmem_barrier``)
+that user kernels inline. Here the device functions live in the CUDA header
+``csrc/include/kraken/ptx_sync.cuh`` (same names; every wait bounded by a deadline) for user CUDA
+kernels to include, and this module offers host-callable launches of them — what a Python user can
+do with a device primitive: run it as a barrier, or run the library's self-test kernels.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from ..ops import lib as _lib
+from ..parallel import symm_mem
+
+HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                      "csrc", "include", "kraken", "ptx_sync.cuh")
+
+
+def symm_mem_sync(signal_pad_ptrs, block_id, rank: int, world_size: int, hasPreviousMemAccess: bool = False,
+                  hasSubsequentMemAccess: bool = False, num_blocks: int = 1) -> torch.Tensor:
+    """Launches `num_blocks` blocks that each run the three barrier patterns (F,T), (T,T), (T,F) of
+    the per-block cross-device barrier with blocks of the same id on all ranks, on the current
+    stream. `signal_pad_ptrs` is a handle (or its ``signal_pad_ptrs_dev``). Returns a uint32 tensor
+    with 1 per block whose waits all completed. The pattern arguments are accepted for signature
+    parity; a host launch has no surrounding kernel whose accesses they would order."""
+    dev_ptr = getattr(signal_pad_ptrs, "signal_pad_ptrs_dev", signal_pad_ptrs)
+    out = torch.zeros(num_blocks, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.lib().kr_sync_test(dev_ptr, rank, world_size, None, out.data_ptr(), 0, num_blocks, 1,
+                                       _lib.current_stream_ptr()))
+    return out
+
+
+def send_signal(handle, dst_rank: int, slot: int, value: int = 1) -> None:
+    """Stream-ordered write of `value` into word `slot` of `dst_rank`'s signal pad (the host-side
+    counterpart of the device function; uses a stream memory operation)."""
+    addr = handle.signal_pad_ptrs[dst_rank] + 4 * slot
+    _lib.check(_lib.lib().kr_stream_write_value32(_lib.current_stream_ptr(), addr, value))
+
+
+def get_flat_tid() -> str:
+    """Device-only in the reference; here: the expression user CUDA code uses."""
+    return "threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z)"
+
+
+def gmem_barrier_test(num_producers: int, num_blocks: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Runs the arrive/wait self-test: blocks [0, num_producers) publish a value and arrive on their
+    flag; the other blocks wait on flag (block % num_producers) and read the value.
+    Returns (flags, values-seen-per-block)."""
+    flags = torch.zeros(num_producers, dtype=torch.int32, device="cuda")
+    out = torch.zeros(num_blocks, dtype=torch.int32, device="cuda")
+    pads = torch.zeros(1, dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().kr_sync_test(pads.data_ptr(), 0, 1, flags.data_ptr(), out.data_ptr(), 1, num_blocks,
+                                       num_producers, _lib.current_stream_ptr()))
+    return flags, out
+
+
+def arrive_gmem_barrier(flag: torch.Tensor, index: int = 0, update: int = 1) -> None:
+    """Stream-ordered flag write (host counterpart of the device function)."""
+    _lib.check(_lib.lib().kr_stream_write_value32(_lib.current_stream_ptr(), flag.data_ptr() + 4 * index, update))
+
+
+def wait_gmem_barrier(flag: torch.Tensor, index: int = 0, expect: int = 1) -> None:
+    """Stream-ordered wait until flag[index] == expect (host counterpart of the device function)."""
+    _lib.check(_lib.lib().kr_stream_wait_value32(_lib.current_stream_ptr(), flag.data_ptr() + 4 * index, expect))
+
+
+def wait_timeout_test(num_blocks: int = 4) -> torch.Tensor:
+    """Blocks wait on flags nothing sets; with a short deadline they give up, record a status word
+    and return. Returns per-block results (2 = gave up)."""
+    flags = torch.zeros(num_blocks, dtype=torch.int32, device="cuda")
+    out = torch.zeros(num_blocks, dtype=torch.int32, device="cuda")
+    pads = torch.zeros(1, dtype=torch.int64, device="cuda")
+    _lib.check(_lib.lib().kr_sync_test(pads.data_ptr(), 0, 1, flags.data_ptr(), out.data_ptr(), 2, num_blocks, 1,
+                                       _lib.current_stream_ptr()))
+    return out
+
+
+__all__ = ["symm_mem_sync", "send_signal", "get_flat_tid", "arrive_gmem_barrier", "wait_gmem_barrier",
+           "gmem_barrier_test", "wait_timeout_test", "HEADER"]

@@ -1,0 +1,73 @@
+"""Environment-backed settings of the library (the reference has only kwargs and three env vars:
+``BENCHMARK_ITERS``, ``NO_TRACE``, ``SYMM_DUMP_KERNEL`` — kraken/_logging/benchmarking.py:34,49,
+kraken/comm/two_shot_all_reduce.py:153).
+
+=========================  ==========================================================================
+``KRAKEN_SYNC_TIMEOUT_MS``  deadline of every device-side wait (default 4000)
+``KRAKEN_NVLS``             ``0`` disables NVLS multicast binding and the multimem kernels (default 1)
+``KRAKEN_SIGNAL_PAD_BYTES`` signal-pad size of blocks from the native allocator (default 1 MiB)
+``KRAKEN_FORCE_ALGO``       ``one_shot`` / ``two_shot`` / ``multimem``: overrides all-reduce selection
+``KRAKEN_NUM_COMM_SMS``     comm CTAs of the fused all-gather GEMM (default 8)
+``KRAKEN_AG_MODE``          ``sm`` (in-kernel pull, default) or ``ce`` (copy engine + stream flags)
+``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
+``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
+``BENCHMARK_ITERS``         overrides the iteration count of the timing harness
+=========================  ==========================================================================
+"""
+from __future__ import annotations
+
+import os
+
+
+def _env_int(name: str, default: int) -> int:
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def sync_timeout_ms() -> float:
+    try:
+        return float(os.environ.get("KRAKEN_SYNC_TIMEOUT_MS", 4000))
+    except ValueError:
+        return 4000.0
+
+
+def nvls_enabled() -> bool:
+    return os.environ.get("KRAKEN_NVLS", "1") != "0"
+
+
+def signal_pad_bytes() -> int:
+    v = _env_int("KRAKEN_SIGNAL_PAD_BYTES", 1 << 20)
+    return max(16384, (v + 15) // 16 * 16)
+
+
+def force_algo() -> str | None:
+    v = os.environ.get("KRAKEN_FORCE_ALGO", "").strip().lower()
+    return v or None
+
+
+def num_comm_sms() -> int:
+    return max(1, _env_int("KRAKEN_NUM_COMM_SMS", 8))
+
+
+def ag_mode() -> str:
+    v = os.environ.get("KRAKEN_AG_MODE", "sm").strip().lower()
+    return v if v in ("sm", "ce") else "sm"
+
+
+def dump_kernel() -> bool:
+    return os.environ.get("KRAKEN_DUMP_KERNEL", "0") == "1"
+
+
+def symm_backend() -> str:
+    v = os.environ.get("KRAKEN_SYMM_BACKEND", "native").strip().lower()
+    return v if v in ("native", "torch") else "native"
+
+
+# Signal-pad layout (uint32 words). Words [0, BARRIER_WORDS) are per-block barrier slots
+# (slot = block_id * world_size + src_rank, the reference's layout); the fused GEMM kernels keep
+# their per-tile flags from TILE_FLAG_BASE on. A 9216-byte pad (torch's default) only has the
+# barrier region, which is all the memory-bound kernels need.
+BARRIER_WORDS = 2304
+TILE_FLAG_BASE = 4096

@@ -1,0 +1,32 @@
+"""Communication fused with compute (reference: kraken/fused/__init__.py:1-27; like the reference,
+``gemm_one_shot_all_reduce`` is also exported as ``gemm_one_shot_all_reduce_fused``)."""
+from .all_reduce_bias import (
+    one_shot_all_reduce_bias,
+    one_shot_all_reduce_bias_rms_norm,
+    two_shot_all_reduce_bias,
+    two_shot_all_reduce_bias_rms_norm,
+)
+from .gemm_ops import (
+    all_gather_matmul,
+    gemm_one_shot_all_reduce,
+    gemm_reduce_scatter,
+    gemm_reduce_scatter_ce_persistent,
+    matmul,
+)
+from .rms_norm import rms_norm
+
+gemm_one_shot_all_reduce_fused = gemm_one_shot_all_reduce
+
+__all__ = [
+    "all_gather_matmul",
+    "gemm_one_shot_all_reduce",
+    "gemm_one_shot_all_reduce_fused",
+    "gemm_reduce_scatter",
+    "gemm_reduce_scatter_ce_persistent",
+    "matmul",
+    "one_shot_all_reduce_bias",
+    "one_shot_all_reduce_bias_rms_norm",
+    "rms_norm",
+    "two_shot_all_reduce_bias",
+    "two_shot_all_reduce_bias_rms_norm",
+]

@@ -1,0 +1,236 @@
+"""Fused GEMM + collective ops on the tcgen05 kernels.
+
+Signatures follow the reference: kraken/fused/all_gather_matmul.py:222-325,
+kraken/fused/gemm_one_shot_all_reduce_fused.py:106-178,
+kraken/fused/gemm_reduce_scatter_fused.py:152-235,
+kraken/fused/gemm_reduce_scatter_ce_persistent.py:326-375. The Triton tiling kwargs
+(``block_size_*``, ``BLOCK_SIZE_*``, ``group_size_m``, ``num_stages``, ``num_warps``) are accepted and
+ignored: tile shapes are chosen by the library (128 x 256 x 64, or 128 x {16..128} with the
+operands swapped for decode-sized M).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _reference as ref
+from .. import config
+from ..ops import lib as _lib
+from ..parallel import symm_mem
+from .gemm_common import as_k_major_a, as_k_major_bt
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, **kwargs) -> torch.Tensor:
+    """Single-GPU C = A @ B on the library's tcgen05 kernel (bf16 inputs, fp32 accumulate).
+    Not in the reference's API; it is the compute core of every fused op, exposed for tests and
+    roofline measurements. kwargs: swap_ab (-1 auto / 0 / 1), bn (column-tile override), max_ctas."""
+    if a.device.type != "cuda":
+        return ref.matmul_f32(a, b).to(out_dtype)
+    a2, lda = as_k_major_a(a)
+    bt, ldb = as_k_major_bt(b)
+    M, K = a2.shape
+    N = bt.shape[0]
+    if bt.shape[1] != K:
+        raise ValueError("inner dimensions differ")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("output must be bfloat16 or float32")
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _lib.check(_lib.lib().kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
+                                       1 if out_dtype == torch.float32 else 0, int(kwargs.get("swap_ab", -1)),
+                                       int(kwargs.get("bn", 0)), int(kwargs.get("max_ctas", 0)),
+                                       _lib.current_stream_ptr()))
+    return out
+
+
+_ag_counters: dict[int, torch.Tensor] = {}
+
+
+def _zero_counters(device: torch.device, n: int, emu) -> torch.Tensor:
+    if emu is not None:
+        t = torch.zeros(n, dtype=torch.int32, device=device)
+        emu._keep.append(t)
+        return t
+    t = _ag_counters.get(device.index)
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 1024), dtype=torch.int32, device=device)
+        _ag_counters[device.index] = t
+    return t
+
+
+def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tensor | None = None,
+                      progress: torch.Tensor | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
+    """(gathered A [M, K], C [M, N] = gathered A @ b). `a_shared` is this rank's [M/ws, K] shard in
+    symmetric memory. One kernel: comm CTAs pull the peers' shards chunk by chunk into `a_out` and
+    raise `progress` flags, MMA CTAs begin with the local shard and follow the flags.
+    kwargs: splits_per_rank=1, num_comm_sms, backend="sm"|"ce" (copy engine + stream flags as in
+    the reference), group."""
+    group = kwargs.get("group")
+    if a_shared.device.type != "cuda":
+        a, c = ref.all_gather_matmul(a_shared, b, group)
+        if progress is not None:
+            progress.fill_(1)
+        if a_out is not None:
+            a_out.copy_(a)
+            a = a_out
+        return a, c
+    if a_shared.dtype != torch.bfloat16 or not a_shared.is_contiguous():
+        raise TypeError("a_shared must be a contiguous bfloat16 symmetric tensor")
+    hdl = symm_mem.rendezvous(a_shared, group)
+    ws, rank = hdl.world_size, hdl.rank
+    shard_rows, K = a_shared.shape
+    M = shard_rows * ws
+    bt, ldb = as_k_major_bt(b)
+    N = bt.shape[0]
+    if bt.shape[1] != K or K % 8:
+        raise ValueError("inner dimensions must match and be a multiple of 8")
+    splits = int(kwargs.get("splits_per_rank", 1))
+    if shard_rows % splits:
+        splits = 1
+    if a_out is None:
+        a_out = torch.empty((M, K), dtype=a_shared.dtype, device=a_shared.device)
+    if progress is None:
+        progress = torch.zeros(ws * splits, dtype=torch.uint32, device=a_shared.device)
+    else:
+        progress.zero_()
+    c = torch.empty((M, N), dtype=a_shared.dtype, device=a_shared.device)
+    backend = kwargs.get("backend", config.ag_mode())
+    counters = _zero_counters(a_shared.device, ws * splits, hdl.group.emu)
+    L = _lib.lib()
+    off = hdl.offset_of(a_shared)
+    if off:
+        raise ValueError("a_shared must start at the beginning of its symmetric buffer")
+    if backend == "ce" and hdl.group.emu is None and ws > 1:
+        from ..comm.all_gather import _copy_engine_all_gather_w_progress
+
+        stream = _copy_engine_all_gather_w_progress(a_out, a_shared, progress, splits)
+        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
+                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
+                                     progress.data_ptr(), counters.data_ptr(), -1, 0, _lib.current_stream_ptr()))
+        torch.cuda.current_stream().wait_stream(stream)
+    else:
+        n_comm = int(kwargs.get("num_comm_sms", config.num_comm_sms()))
+        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
+                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
+                                     progress.data_ptr(), counters.data_ptr(), n_comm, 0, _lib.current_stream_ptr()))
+    return a_out, c
+
+
+def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
+    """fp32 [M, N] = all_reduce(a @ b): each rank holds a K-shard of both operands. The fp32
+    partial tile goes to the rank's symmetric staging buffer, per-tile flags replace a grid-wide
+    barrier, and every rank sums each tile from all ranks in rank order (identical results on all
+    ranks). Decode-sized M puts the weights on the 128-row side of the MMA."""
+    group = kwargs.get("group")
+    if a.device.type != "cuda":
+        return ref.gemm_all_reduce(a, b, group)
+    a2, lda = as_k_major_a(a)
+    bt, ldb = as_k_major_bt(b)
+    M, K = a2.shape
+    N = bt.shape[0]
+    if bt.shape[1] != K or K % 8:
+        raise ValueError("inner dimensions must match and be a multiple of 8")
+    info = symm_mem.resolve_group(group)
+    out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    L = _lib.lib()
+    if info.world_size == 1:
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0,
+                                  _lib.current_stream_ptr()))
+        return out
+    hdl = symm_mem.get_symm_mem_workspace(group, M * N * 4, a.device)
+    _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, a2.data_ptr(),
+                                 lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, int(kwargs.get("swap_ab", -1)),
+                                 0, config.TILE_FLAG_BASE, hdl.signal_pad_words, _lib.current_stream_ptr()))
+    return out
+
+
+def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
+    """[M/ws, N] = reduce_scatter(a @ b) along M. The GEMM epilogue pushes every finished tile
+    into its owner's staging slab over NVLink; owners sum the ws slabs in rank order. Shapes whose
+    slab is not a multiple of 128 rows run GEMM -> symmetric staging -> reduce-scatter kernel."""
+    group = kwargs.get("group")
+    if a.device.type != "cuda":
+        return ref.gemm_reduce_scatter(a, b, group)
+    a2, lda = as_k_major_a(a)
+    bt, ldb = as_k_major_bt(b)
+    M, K = a2.shape
+    N = bt.shape[0]
+    if bt.shape[1] != K or K % 8:
+        raise ValueError("inner dimensions must match and be a multiple of 8")
+    info = symm_mem.resolve_group(group)
+    ws = info.world_size
+    if M % ws:
+        raise ValueError("M must be divisible by the world size")
+    out_dtype = a.dtype if a.dtype in (torch.bfloat16,) else torch.bfloat16
+    out = torch.empty((M // ws, N), dtype=out_dtype, device=a.device)
+    L = _lib.lib()
+    s = _lib.current_stream_ptr()
+    if ws == 1:
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, s))
+    elif (M // ws) % 128 == 0 and N % 8 == 0:
+        hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
+        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, hdl.rank, ws, a2.data_ptr(), lda,
+                                     bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, config.TILE_FLAG_BASE,
+                                     hdl.signal_pad_words, s))
+    else:
+        if (M * N) % (8 * ws):
+            raise ValueError("M * N must be a multiple of 8 * world size")
+        hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
+        stage = hdl.buffer_ptrs[hdl.rank]
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, s))
+        _lib.check(L.kr_reduce_scatter(hdl.buffer_ptrs_dev, 0, hdl.signal_pad_ptrs_dev, hdl.rank, ws, None,
+                                       out.data_ptr(), M * N, 0, 0, s))
+    return out if out.dtype == a.dtype or a.dtype != torch.float32 else out.to(a.dtype)
+
+
+_ce_state: dict[int, tuple] = {}
+
+
+def gemm_reduce_scatter_ce_persistent(a: torch.Tensor, b: torch.Tensor, reduce_op: str = "sum", group=None,
+                                      **kwargs) -> torch.Tensor:
+    """Copy-engine variant of GEMM -> reduce-scatter (the reference's recipe): a persistent producer
+    GEMM writes the local product slab by slab (next rank's slab first) and raises a signal word
+    per finished slab; on a backend stream, stream waits on those words gate copy-engine transfers
+    of each slab to its owner's workspace; after a cross-device barrier a local kernel sums the ws
+    received slabs."""
+    if reduce_op != "sum":
+        raise ValueError("only reduce_op='sum' is supported")
+    if a.device.type != "cuda":
+        return ref.gemm_reduce_scatter(a, b, group)
+    a2, lda = as_k_major_a(a)
+    bt, ldb = as_k_major_bt(b)
+    M, K = a2.shape
+    N = bt.shape[0]
+    info = symm_mem.resolve_group(group)
+    ws, rank = info.world_size, info.rank
+    if M % ws or (M // ws) % 128:
+        raise ValueError("copy-engine GEMM reduce-scatter needs (M / world_size) % 128 == 0")
+    L = _lib.lib()
+    dev = a.device
+    out = torch.empty((M // ws, N), dtype=torch.bfloat16, device=dev)
+    if ws == 1:
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0,
+                                  _lib.current_stream_ptr()))
+        return out
+    gemm_out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, dev)
+    backend = symm_mem._get_backend_stream(priority=-1)
+    cur = torch.cuda.current_stream()
+    signals = torch.zeros(ws, dtype=torch.uint32, device=dev)
+    counters = torch.zeros(ws, dtype=torch.uint32, device=dev)
+    backend.wait_stream(cur)
+    _lib.check(L.kr_gemm_ce_producer_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, gemm_out.data_ptr(), N, M, N, K,
+                                          rank, ws, signals.data_ptr(), counters.data_ptr(), cur.cuda_stream))
+    slab_bytes = (M // ws) * N * 2
+    ptrs = (ctypes.c_void_p * ws)(*hdl.buffer_ptrs)
+    with torch.cuda.stream(backend):
+        _lib.check(L.kr_ce_scatter_slabs(ptrs, rank, ws, gemm_out.data_ptr(), signals.data_ptr(), slab_bytes,
+                                         backend.cuda_stream))
+    cur.wait_stream(backend)
+    hdl.barrier()                       # every rank's slabs have landed everywhere
+    _lib.check(L.kr_reduce_slabs(hdl.buffer_ptrs[rank], out.data_ptr(), ws, (rank + 1) % ws, (M // ws) * N,
+                                 cur.cuda_stream))
+    hdl.barrier()                       # workspace free for the next op
+    for t in (gemm_out, signals, counters):
+        t.record_stream(backend)
+    return out

@@ -1,0 +1,111 @@
+"""Ahead-of-time build of the native library (CUDA kernels + C++ runtime) for sm_100a.
+
+Every ``csrc/*.cu`` file is compiled with ``nvcc -gencode arch=compute_100a,code=sm_100a`` into an
+object file and linked into ``kraken_b200/_C/libkraken_b200.so`` in the source tree, so the
+library travels with the checkout and no JIT cache is involved. A source hash stored next to the
+library makes rebuilds incremental. nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parents[2]
+CSRC = REPO / "csrc"
+OUT_DIR = REPO / "kraken_b200" / "_C"
+LIB_PATH = OUT_DIR / "libkraken_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-std=c++17", "-O3", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+    "-Xcompiler", "-fvisibility=hidden",
+    f"-I{CSRC / 'include'}",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or put /usr/local/cuda/bin on PATH")
+
+
+def _headers_digest() -> str:
+    h = hashlib.sha256()
+    for p in sorted((CSRC / "include").rglob("*")):
+        if p.is_file():
+            h.update(p.name.encode())
+            h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _source_digest(src: Path, headers: str) -> str:
+    h = hashlib.sha256()
+    h.update(headers.encode())
+    h.update(src.read_bytes())
+    return h.hexdigest()
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compiles what changed and links the shared library. Returns its path."""
+    OUT_DIR.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+    headers = _headers_digest()
+    jobs = []
+    objects = []
+    for src in sources():
+        obj = OUT_DIR / (src.stem + ".o")
+        stamp = OUT_DIR / (src.stem + ".hash")
+        digest = _source_digest(src, headers)
+        objects.append(obj)
+        if not force and obj.exists() and stamp.exists() and stamp.read_text() == digest:
+            continue
+        jobs.append((src, obj, stamp, digest))
+
+    def compile_one(job):
+        src, obj, stamp, digest = job
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            print(" ".join(cmd), file=sys.stderr)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        stamp.write_text(digest)
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(compile_one, jobs))
+    if jobs or not LIB_PATH.exists():
+        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objects), "-Xcompiler", "-fPIC", "-lpthread"]
+        if verbose:
+            print(" ".join(cmd), file=sys.stderr)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB_PATH
+
+
+def is_stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    headers = _headers_digest()
+    for src in sources():
+        stamp = OUT_DIR / (src.stem + ".hash")
+        if not stamp.exists() or stamp.read_text() != _source_digest(src, headers):
+            return True
+    return False
+
+
+if __name__ == "__main__":
+    print(build(verbose=True, force="--force" in sys.argv))
