@@ -1,0 +1,94 @@
+"""All-reduce sweep (reference: benchmark/benchmark_all_reduce.py): bf16 tensors from 4 KB to
+256 MB, one-shot vs two-shot vs NVLS multimem (this library) against NCCL, torch's symmetric-memory
+ops and the reference's Triton kernels. Reports device-timed median microseconds (max over ranks)
+and bus bandwidth 2(n-1)/n * S / t.
+
+    torchrun --nnodes 1 --nproc-per-node N --master-addr 127.0.0.1 benchmark/benchmark_all_reduce.py
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+import torch.distributed as dist
+
+from common import bus_bandwidth_gbs, finish, load_reference, print_table, setup, try_time, NVLINK_GBS_MEASURED
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-bytes", type=int, default=4096)
+    ap.add_argument("--max-bytes", type=int, default=256 << 20)
+    ap.add_argument("--backend", nargs="*", default=None)
+    ap.add_argument("--iters", type=int, default=25)
+    ap.add_argument("--save-path", default="gpurun_out/bench_all_reduce")
+    args = ap.parse_args()
+    rank, ws, dev = setup()
+    from kraken_b200 import comm
+    from kraken_b200.parallel import symm_mem
+    import torch.distributed._symmetric_memory as tsm
+
+    ref, why = load_reference()
+    rows = []
+    nbytes = args.min_bytes
+    while nbytes <= args.max_bytes:
+        numel = nbytes // 2
+        x = torch.randn(numel, device=dev).to(torch.bfloat16)
+        xs = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
+        xs.copy_(x)
+        symm_mem.rendezvous(xs)
+        xm = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
+        xm.copy_(x)
+        symm_mem.rendezvous(xm)
+        golden = x.float().clone()
+        dist.all_reduce(golden)
+        backends = {
+            "one_shot": lambda: comm.one_shot_all_reduce(xs),
+            "two_shot": lambda: comm.two_shot_all_reduce(x),
+            "multimem": lambda: comm.multimem_all_reduce(xm),
+            "nccl": lambda: dist.all_reduce(x.clone()),
+        }
+        try:
+            tx = tsm.empty(numel, dtype=torch.bfloat16, device=dev)
+            tx.copy_(x)
+            tsm.rendezvous(tx, group=dist.group.WORLD)
+            gname = dist.group.WORLD.group_name
+            backends["torch_multimem"] = lambda: torch.ops.symm_mem.multimem_all_reduce_(tx, "sum", gname)
+            backends["torch_one_shot"] = lambda: torch.ops.symm_mem.one_shot_all_reduce(tx, "sum", gname)
+            backends["torch_two_shot"] = lambda: torch.ops.symm_mem.two_shot_all_reduce_(tx, "sum", gname)
+            if ref is not None:
+                backends["ref_triton_one_shot"] = lambda: ref.comm.one_shot_all_reduce(tx)
+                backends["ref_triton_two_shot"] = lambda: ref.comm.two_shot_all_reduce(x)
+        except Exception as e:   # torch symmetric memory unavailable on this box
+            why = why or str(e)
+        if nbytes > (32 << 20):
+            backends.pop("one_shot", None)          # pull traffic (n-1)*S: pointless at this size
+            backends.pop("torch_one_shot", None)
+            backends.pop("ref_triton_one_shot", None)
+        # correctness gate before timing, as the reference's benchmark does
+        torch.testing.assert_close(comm.two_shot_all_reduce(x).float(), golden, atol=1e-1, rtol=1e-1)
+        if "one_shot" in backends:
+            torch.testing.assert_close(comm.one_shot_all_reduce(xs).float(), golden, atol=1e-1, rtol=1e-1)
+        row = {"bytes": nbytes}
+        for name, fn in backends.items():
+            if args.backend and name not in args.backend:
+                continue
+            if name == "multimem":
+                xm.copy_(x)
+            us, err = try_time(fn, iters=args.iters)
+            row[name + "_us"] = us
+            if us:
+                row[name + "_busGBs"] = bus_bandwidth_gbs("all_reduce", nbytes, ws, us)
+        best = min((row[k] for k in ("one_shot_us", "two_shot_us", "multimem_us") if row.get(k)), default=None)
+        if best:
+            row["best_busGBs"] = bus_bandwidth_gbs("all_reduce", nbytes, ws, best)
+            row["frac_of_link"] = row["best_busGBs"] / NVLINK_GBS_MEASURED
+        rows.append(row)
+        nbytes *= 4
+    cols = ["bytes"] + sorted({k for r in rows for k in r if k != "bytes"})
+    print_table(rows, cols, f"all_reduce sweep, {ws} x B200 (us = median, max over ranks)", f"{args.save_path}_ws{ws}")
+    finish()
+
+
+if __name__ == "__main__":
+    main()

@@ -505,3 +505,17 @@ class EmuWorld:
                 with self.rank(r):
                     outs.append(fn(r))
         return outs
+
+
+def reset_signal_pads(handle: SymmHandle) -> None:
+    """Recovery after a reported timeout: a wait that gave up can leave tokens behind in the
+    signal pads. Collective over the handle's group: every rank zeroes its own pad between two
+    process-group barriers (host side), after which the barrier protocol starts clean again."""
+    pg = handle.group.pg
+    torch.cuda.synchronize()
+    if pg is not None:
+        dist.barrier(group=pg)
+    handle.get_signal_pad(handle.rank).zero_()
+    torch.cuda.synchronize()
+    if pg is not None:
+        dist.barrier(group=pg)

@@ -1,0 +1,213 @@
+"""Multi-GPU tests (2 to 4 ranks, one process per GPU, NCCL for bootstrap and goldens): the native
+symmetric allocator's rendezvous, every comm op, every fused op, and the timeout path when a rank
+skips a collective. Mirrors the reference's test matrix (test/test_allreduce.py, test_allgather.py,
+test_allgather_matmul.py, test_allreduce_bias.py, test_allreduce_bias_rms_norm.py,
+test_gemm_allreduce.py, test_gemm_reduce_scatter.py, test_ptx_utils.py) with goldens from NCCL
+collectives and fp32 PyTorch matmuls. Skipped when fewer than 2 GPUs are visible."""
+import os
+
+import pytest
+import torch
+
+from helpers import run_distributed
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _rms_ref(x, w, eps):
+    xf = x.float()
+    return xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+
+def _all_ops(rank, ws):
+    import torch.distributed as dist
+
+    import kraken_b200
+    from kraken_b200 import _ptx_utils as ptx
+    from kraken_b200 import comm, fused
+    from kraken_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+
+    def nccl_sum(t):
+        y = t.float().clone()
+        dist.all_reduce(y)
+        return y
+
+    # -- allocator round trip: every rank reads every peer's buffer directly
+    t = symm_mem.empty(4096, dtype=torch.float32, device=dev)
+    t.fill_(float(rank + 1))
+    hdl = symm_mem.rendezvous(t)
+    assert hdl.rank == rank and hdl.world_size == ws
+    hdl.barrier()
+    for peer in range(ws):
+        v = hdl.get_buffer(peer, (4096,), torch.float32)
+        assert float(v[0]) == float(peer + 1) and float(v[-1]) == float(peer + 1)
+    hdl.barrier()
+    # -- barrier self-test: pads return to zero
+    ok = ptx.symm_mem_sync(hdl, None, rank, ws, num_blocks=32)
+    torch.cuda.synchronize()
+    assert bool((ok == 1).all())
+    dist.barrier()
+    assert int(hdl.get_signal_pad(rank).to(torch.int64).abs().sum()) == 0
+    # -- all-reduce family, [1024, 1024] bf16 (reference: test/test_allreduce.py)
+    x = torch.randn(1024, 1024, device=dev).to(torch.bfloat16)
+    gold = nccl_sum(x)
+    xs = symm_mem.empty(1024, 1024, dtype=torch.bfloat16, device=dev)
+    xs.copy_(x)
+    for _ in range(3):
+        torch.testing.assert_close(comm.one_shot_all_reduce(xs).float(), gold, atol=1e-1, rtol=1e-1)
+        torch.testing.assert_close(comm.two_shot_all_reduce(x).float(), gold, atol=1e-1, rtol=1e-1)
+    z = symm_mem.empty(1024, 1024, dtype=torch.bfloat16, device=dev)
+    z.copy_(x)
+    symm_mem.rendezvous(z)
+    dist.barrier()
+    comm.multimem_all_reduce(z)
+    torch.testing.assert_close(z.float(), gold, atol=1e-1, rtol=1e-1)
+    torch.testing.assert_close(comm.all_reduce(x).float(), gold, atol=1e-1, rtol=1e-1)
+    # -- reduce-scatter
+    rs = comm.reduce_scatter(x)
+    n = 1024 // ws
+    torch.testing.assert_close(rs.float(), gold[rank * n:(rank + 1) * n], atol=1e-1, rtol=1e-1)
+    rs2 = comm.reduce_scatter(xs)
+    assert torch.equal(rs, rs2)
+    # -- all-gather with progress, both engines (reference: test/test_allgather.py)
+    outs = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(outs, x)
+    gold_ag = torch.cat(outs, 0)
+    for backend in ("ce", "sm"):
+        for splits in (1, 4):
+            prog = torch.zeros(ws * splits, dtype=torch.uint32, device=dev)
+            ag = comm.all_gather_w_progress(xs, progress=prog, splits_per_rank=splits, backend=backend)
+            torch.cuda.synchronize()
+            assert torch.equal(ag, gold_ag), (backend, splits)
+            assert bool((prog.to(torch.int64) != 0).all())
+    # -- bias and bias + RMSNorm epilogues (reference: test/test_allreduce_bias*.py)
+    pad = symm_mem.empty(1024, 1024, dtype=torch.bfloat16, device=dev)
+    symm_mem.rendezvous(pad)
+    D = 5120
+    g = torch.Generator().manual_seed(7)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
+    for b in (1, 2, 8, 64):
+        xb = torch.randn(b, D, device=dev).to(torch.bfloat16)
+        bias = torch.randn(b, D, generator=g).to(torch.bfloat16).to(dev)     # same on every rank
+        bias_row = torch.randn(D, generator=g).to(torch.bfloat16).to(dev)
+        s = nccl_sum(xb)
+        for bb in (bias, bias_row, None):
+            goldb = s + (bb.float() if bb is not None else 0.0)
+            out = torch.empty_like(xb)
+            fused.one_shot_all_reduce_bias(pad, xb, bb, out)
+            torch.testing.assert_close(out.float(), goldb, atol=5e-2, rtol=5e-2)
+            out2 = torch.empty_like(xb)
+            fused.two_shot_all_reduce_bias(pad, xb, bb, out2)
+            torch.testing.assert_close(out2.float(), goldb, atol=5e-2, rtol=5e-2)
+        for bb in (bias, bias_row):
+            goldn = _rms_ref(s + bb.float(), w, 1e-5)
+            for fn in (fused.one_shot_all_reduce_bias_rms_norm, fused.two_shot_all_reduce_bias_rms_norm):
+                y = torch.empty_like(xb)
+                fn(pad, xb, bb, w, y, 1e-5)
+                torch.testing.assert_close(y.float(), goldn, atol=4e-2, rtol=4e-2)
+    # -- all-gather matmul (reference: test/test_allgather_matmul.py, scaled down)
+    Ml, K, N = 1024, 2048, 1536
+    a_sh = symm_mem.empty(Ml, K, dtype=torch.bfloat16, device=dev)
+    a_sh.copy_(torch.randn(Ml, K, device=dev).to(torch.bfloat16))
+    bt = (0.05 * torch.randn(N, K, device=dev)).to(torch.bfloat16)
+    parts = [torch.empty_like(a_sh) for _ in range(ws)]
+    dist.all_gather(parts, a_sh)
+    a_full = torch.cat(parts, 0)
+    gold_c = a_full.float() @ bt.float().t()
+    for backend in ("sm", "ce"):
+        for splits in (1, 2):
+            for _ in range(2):
+                ag, c = fused.all_gather_matmul(a_sh, bt.t(), splits_per_rank=splits, backend=backend)
+                torch.cuda.synchronize()
+                assert torch.equal(ag, a_full), (backend, splits)
+                torch.testing.assert_close(c.float(), gold_c, atol=1e-1, rtol=1e-1)
+    # -- GEMM + reduce-scatter, both variants (reference: test/test_gemm_reduce_scatter.py)
+    M, Kl, N2 = 256 * ws, 1024, 1024
+    a = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
+    bt2 = (0.05 * torch.randn(N2, Kl, device=dev)).to(torch.bfloat16)
+    full = nccl_sum(a.float() @ bt2.float().t())
+    ms = M // ws
+    for fn in (fused.gemm_reduce_scatter, fused.gemm_reduce_scatter_ce_persistent):
+        for _ in range(3):
+            r = fn(a, bt2.t())
+            torch.testing.assert_close(r.float(), full[rank * ms:(rank + 1) * ms], atol=1e-1, rtol=5e-2)
+    a_u = torch.randn(64 * ws, 256, device=dev).to(torch.bfloat16)          # slab not a multiple of 128
+    bt_u = (0.05 * torch.randn(512, 256, device=dev)).to(torch.bfloat16)
+    full_u = nccl_sum(a_u.float() @ bt_u.float().t())
+    r = fused.gemm_reduce_scatter(a_u, bt_u.t())
+    torch.testing.assert_close(r.float(), full_u[rank * 64:(rank + 1) * 64], atol=1e-1, rtol=5e-2)
+    # -- GEMM + all-reduce for decode shapes (reference: test/test_gemm_allreduce.py)
+    for Md in (1, 16, 64, 256):
+        ad = torch.randn(Md, 1024, device=dev).to(torch.bfloat16)
+        btd = (0.02 * torch.randn(2048, 1024, device=dev)).to(torch.bfloat16)
+        gold_d = nccl_sum(ad.float() @ btd.float().t())
+        for _ in range(2):
+            o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t())
+            assert o.dtype == torch.float32
+            torch.testing.assert_close(o, gold_d, atol=5e-3, rtol=5e-3)
+    ones = torch.ones(32, 32, device=dev, dtype=torch.bfloat16)
+    o = fused.gemm_one_shot_all_reduce_fused(ones * (rank + 1), ones)
+    expect = 32.0 * sum(range(1, ws + 1))
+    torch.testing.assert_close(o, torch.full((32, 32), expect, device=dev), atol=1e-5, rtol=1e-5)
+    # -- the model block
+    mlp = kraken_b200.models.TPMLP(hidden=1024, ffn=2048 * ws, device=dev, seed=11)
+    xm = mlp.stage_input(torch.randn(256, 1024, device=dev).to(torch.bfloat16))
+    dist.barrier()
+    y = mlp.prefill(xm)
+    assert y.shape == (256, 1024) and bool(torch.isfinite(y.float()).all())
+    torch.cuda.synchronize()
+    kraken_b200.check_status()
+    dist.barrier()
+
+
+def _rank_skips_collective(rank, ws):
+    # Host-made failure: rank 1 does not take part in one all-reduce. Rank 0's kernel waits for a
+    # signal that never comes, gives up at its deadline, reports it through the status word and the
+    # context stays usable. NVLS is off in this test (KRAKEN_NVLS=0, NCCL_NVLS_ENABLE=0).
+    import torch.distributed as dist
+
+    import kraken_b200
+    from kraken_b200 import comm
+    from kraken_b200.ops import lib as klib
+    from kraken_b200.parallel import symm_mem
+
+    dev = torch.device("cuda", rank)
+    x = symm_mem.empty(1024, dtype=torch.bfloat16, device=dev)
+    x.fill_(1.0)
+    hdl = symm_mem.rendezvous(x)
+    assert not hdl.multicast_ptr
+    dist.barrier()
+    torch.testing.assert_close(comm.one_shot_all_reduce(x).float(), torch.full((1024,), float(ws), device=dev))
+    torch.cuda.synchronize()
+    dist.barrier()
+    klib.check(klib.lib().kr_set_timeout_ms(300.0))
+    if rank == 0:
+        comm.one_shot_all_reduce(x)
+        with pytest.raises(kraken_b200.KrakenSyncTimeout):
+            kraken_b200.check_status()
+        assert float(torch.ones(4, device=dev).sum()) == 4.0      # context still alive
+    torch.cuda.synchronize()
+    dist.barrier()                                                   # the others learn of it on the host
+    symm_mem.reset_signal_pads(hdl)
+    klib.check(klib.lib().kr_set_timeout_ms(4000.0))
+    torch.testing.assert_close(comm.one_shot_all_reduce(x).float(), torch.full((1024,), float(ws), device=dev))
+    torch.cuda.synchronize()
+    kraken_b200.check_status()
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_all_ops_multi_gpu():
+    run_distributed(_all_ops, min(_ngpu(), 4), "nccl")
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_missing_rank_times_out_on_gpu(monkeypatch):
+    monkeypatch.setenv("KRAKEN_NVLS", "0")
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    run_distributed(_rank_skips_collective, 2, "nccl")
