@@ -10,6 +10,8 @@
 // kraken/fused/two_shot_all_reduce_bias.py:24-193, kraken/comm/copy_engine_all_gather.py:6-126.
 // multimem_all_reduce and reduce_scatter have no reference kernel (the reference only names them).
 #include <map>
+#include <mutex>
+#include <string>
 #include "kraken/host.h"
 #include "kraken/vec.cuh"
 
@@ -497,4 +499,97 @@ KR_API int kr_symm_barrier(uint32_t* const* pads, int rank, int ws, int slot, cu
   p.mode = slot;
   p.sync = sync_ctx(d);
   return launch_ranked(symm_barrier_kernel, symm_barrier_emu_kernel, p, 1, 128, 0, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the SM all-gather (declared in kraken/no_alloc.h). The arrival
+// counters and a status word live in a fixed device array instead of allocated memory.
+// ---------------------------------------------------------------------------------------------
+#include "kraken/no_alloc.h"
+
+namespace kraken {
+constexpr int kNoAllocStatusWords = 64;   // 256 bytes: word 0 is the default status word
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocStatusWords + KR_NOALLOC_MAX_CHUNKS];
+static_assert(sizeof(uint32_t) * (kNoAllocStatusWords + KR_NOALLOC_MAX_CHUNKS) == KR_NOALLOC_SCRATCH_BYTES,
+              "scratch size stated in the header");
+
+struct NoAllocDevice {
+  bool ready = false;
+  uint32_t* scratch = nullptr;   // DEVICE address of g_noalloc_scratch on this device
+  int num_sms = 0;
+};
+static NoAllocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_mu;
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address: the
+// address a kernel can use has to be asked for, per device, with that device current.
+static int noalloc_device(NoAllocDevice** out) {
+  int dev = -1;
+  KR_CUDA(cudaGetDevice(&dev));
+  KR_REQUIRE(dev >= 0 && dev < 64, "device index out of range");
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.ready) {
+    void* ptr = nullptr;
+    KR_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    KR_CUDA(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev));
+    d.scratch = (uint32_t*)ptr;
+    d.ready = true;
+  }
+  *out = &d;
+  return KR_SUCCESS;
+}
+
+static uint64_t noalloc_timeout_ns() {
+  const char* e = getenv("KRAKEN_SYNC_TIMEOUT_MS");
+  double ms = e ? atof(e) : 4000.0;
+  if (ms <= 0) ms = 4000.0;
+  return (uint64_t)(ms * 1e6);
+}
+}  // namespace kraken
+
+KR_API int kr_all_gather_sm_noalloc(void* const* bufs, unsigned long long buf_off, uint32_t* const* pads, int rank,
+                                    int world_size, void* output, uint32_t* progress, int splits,
+                                    unsigned long long numel, int max_blocks, uint32_t pad_base, uint32_t* status,
+                                    cudaStream_t stream) {
+  const int ws = world_size;
+  KR_REQUIRE(ws >= 1 && ws <= 72 && rank >= 0 && rank < ws, "bad rank/world size");
+  KR_REQUIRE(splits >= 1 && numel % (8ull * splits) == 0, "all-gather needs numel % (8 * splits) == 0");
+  if ((unsigned long long)ws * (unsigned long long)splits > KR_NOALLOC_MAX_CHUNKS)
+    return fail(KR_FAIL_ARG, "kr_all_gather_sm_noalloc: world_size * splits = " + std::to_string((long long)ws * splits) +
+                                 " exceeds the built-in scratch of " + std::to_string(KR_NOALLOC_MAX_CHUNKS) +
+                                 " chunks; use kr_all_gather_sm with caller-provided counters");
+  KR_REQUIRE(pad_base % ws == 0, "pad_base must be a multiple of the world size");
+  KR_REQUIRE(buf_off % 16 == 0 && ((uintptr_t)output & 15) == 0, "tensors must be 16-byte aligned");
+  KR_REQUIRE(bufs && pads && output && progress, "null argument");
+  KR_REQUIRE(!emu_recorder().active, "not available while rank emulation is recording");
+  NoAllocDevice* d = nullptr;
+  int rc = noalloc_device(&d);
+  if (rc) return rc;
+  uint32_t* counters = d->scratch + kNoAllocStatusWords;
+  // the array keeps whatever the previous call left: counters must start at zero
+  KR_CUDA(cudaMemsetAsync(counters, 0, sizeof(uint32_t) * (size_t)ws * splits, stream));
+  CommParams p;
+  memset(&p, 0, sizeof(p));
+  p.bufs = bufs;
+  p.buf_off = buf_off;
+  p.pads = pads;
+  p.rank = rank;
+  p.ws = ws;
+  p.numel = numel;
+  p.bias_period = 8;
+  p.pad_base = pad_base;
+  p.splits = splits;
+  p.output = output;
+  p.progress = progress;
+  p.counters = counters;
+  p.sync = SyncCtx{status ? status : d->scratch, noalloc_timeout_ns()};
+  unsigned nb = cdiv(numel / 8 / splits, kCommThreads * 4);
+  unsigned cap = (unsigned)d->num_sms;
+  if (max_blocks > 0 && (unsigned)max_blocks < cap) cap = (unsigned)max_blocks;
+  if (nb < 1) nb = 1;
+  if (nb > cap) nb = cap;
+  void* args[] = {(void*)&p};
+  KR_CUDA(cudaLaunchKernel((const void*)all_gather_kernel, dim3(nb), dim3(kCommThreads), args, 0, stream));
+  return KR_SUCCESS;
 }

@@ -72,6 +72,8 @@ _PROTOS = {
     "kr_two_shot_all_reduce": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, _P, c_ulonglong, c_ulonglong, _P, c_int, c_uint32, _P]),
     "kr_reduce_scatter": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, c_ulonglong, c_int, c_uint32, _P]),
     "kr_all_gather_sm": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, _P, c_int, c_ulonglong, c_int, c_uint32, _P]),
+    "kr_all_gather_sm_noalloc": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, c_int, c_ulonglong, c_int, c_uint32,
+                                         _P, _P]),
     "kr_symm_barrier": (c_int, [_P, c_int, c_int, c_int, _P]),
     "kr_sync_test": (c_int, [_P, c_int, c_int, _P, _P, c_int, c_int, c_int, _P]),
     # norm kernels
