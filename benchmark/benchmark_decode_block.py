@@ -1,0 +1,81 @@
+"""Decode-shaped chain (no reference script; the shapes come from the tensor-parallel decode use
+case the reference's ops target): gemm_one_shot_all_reduce_fused with A bf16 [M, 8192/ws],
+B bf16 [8192/ws, 8192], M in {1, 16, 64, 256}, then two_shot_all_reduce_bias_rms_norm on [M, 8192].
+Baselines: cuBLAS + NCCL all_reduce (fp32), and NCCL all_reduce + add + rms_norm."""
+from __future__ import annotations
+
+import argparse
+
+import torch
+import torch.distributed as dist
+
+from common import finish, load_reference, peaks, print_table, setup, try_time
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--M", type=int, nargs="*", default=[1, 16, 64, 256])
+    ap.add_argument("--K", type=int, default=8192, help="global K; each rank holds K / world_size")
+    ap.add_argument("--N", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--save-path", default="gpurun_out/bench_decode_block")
+    args = ap.parse_args()
+    rank, ws, dev = setup()
+    from kraken_b200 import fused
+    from kraken_b200.parallel import symm_mem
+    import torch.distributed._symmetric_memory as tsm
+
+    ref, why = load_reference()
+    pk = peaks()
+    Kl, N = args.K // ws, args.N
+    bt = (0.02 * torch.randn(N, Kl, device=dev)).to(torch.bfloat16)
+    b = bt.t()
+    g = torch.Generator().manual_seed(3)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16).to(dev)
+    w = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(dev)
+    pad = symm_mem.empty(max(args.M) * N, dtype=torch.bfloat16, device=dev)
+    symm_mem.rendezvous(pad)
+    rows = []
+    for M in args.M:
+        a = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
+        x = torch.randn(M, N, device=dev).to(torch.bfloat16)
+        y = torch.empty_like(x)
+
+        def cublas_nccl():
+            c = torch.matmul(a, b).float()
+            dist.all_reduce(c)
+            return c
+
+        def nccl_norm():
+            t = x.clone()
+            dist.all_reduce(t)
+            return fused.rms_norm(t + bias, w, 1e-5)
+
+        gold = cublas_nccl()
+        o = fused.gemm_one_shot_all_reduce_fused(a, b)
+        torch.testing.assert_close(o, gold, atol=5e-2, rtol=5e-2)
+        backends = {
+            "gemm_ar_fused": lambda: fused.gemm_one_shot_all_reduce_fused(a, b),
+            "cublas_nccl": cublas_nccl,
+            "ar_bias_norm_two_shot": lambda: fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
+            "ar_bias_norm_one_shot": lambda: fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
+            "nccl_add_norm": nccl_norm,
+        }
+        if ref is not None and ((M + 63) // 64) * (N // 64) * ws <= 2304:
+            af, bf = a.float(), b.float().contiguous()
+            backends["ref_gemm_ar"] = lambda: ref.fused.gemm_one_shot_all_reduce_fused(af, bf)
+        row = {"M": M, "K_per_rank": Kl, "N": N,
+               "weight_read_us": Kl * N * 2 / (pk["hbm_gbs"] * 1e9) * 1e6}
+        for name, fn in backends.items():
+            us, err = try_time(fn, iters=args.iters, warmup=20)
+            row[name + "_us"] = us
+            if us is None and rank == 0:
+                print(f"[{name}] n/a: {err}", flush=True)
+        rows.append(row)
+    cols = ["M", "K_per_rank", "N", "weight_read_us"] + sorted({k for r in rows for k in r if k.endswith("_us") and k != "weight_read_us"})
+    print_table(rows, cols, f"decode block, {ws} x B200", f"{args.save_path}_ws{ws}")
+    finish()
+
+
+if __name__ == "__main__":
+    main()

@@ -125,40 +125,88 @@ __device__ __forceinline__ void two_shot_ar_impl(const CommParams& p, unsigned b
   } else {
     if (!block_sync_F_T(p, bid, 3)) return;
   }
-  for (size_t g = bid; g < ngroups; g += nb) {
-    size_t v = g * group + (size_t)p.rank * blockDim.x + threadIdx.x;
-    if (v >= nvec) continue;
-    U4 r;
+  // Four chunk groups per iteration: all their loads (4 x ws, or 4 multimem.ld_reduce) are in
+  // flight before the first sum, which is what fills the NVLink pipe.
+  constexpr int UNR = 4;
+  for (size_t g0 = bid; g0 < ngroups; g0 += (size_t)nb * UNR) {
+    size_t vs[UNR];
+    bool act[UNR];
+#pragma unroll
+    for (int k = 0; k < UNR; ++k) {
+      const size_t g = g0 + (size_t)k * nb;
+      vs[k] = g * group + (size_t)p.rank * blockDim.x + threadIdx.x;
+      act[k] = g < ngroups && vs[k] < nvec;
+    }
     if (USE_MC) {
-      r = multimem_ld_reduce_bf16x8((const char*)p.mc_ptr + p.buf_off + v * 16);
-      if (p.bias) {
-        float f[8];
-        unpack8(r, f);
-        add_bias8(p, v * 8, f);
-        r = pack8(f);
-      }
-      multimem_st16((char*)p.mc_ptr + p.buf_off + v * 16, r);
-    } else {
-      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (p.bias) add_bias8(p, v * 8, f);
-      U4 x[8];
-      for (int s0 = 0; s0 < p.ws; s0 += 8) {
+      U4 r[UNR];
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          if (s0 + s < p.ws) {
-            int peer = p.rank + s0 + s;
-            if (peer >= p.ws) peer -= p.ws;
-            x[s] = ld16(symm_buf(p, peer) + v * 16);
+      for (int k = 0; k < UNR; ++k)
+        if (act[k]) r[k] = multimem_ld_reduce_bf16x8((const char*)p.mc_ptr + p.buf_off + vs[k] * 16);
+#pragma unroll
+      for (int k = 0; k < UNR; ++k)
+        if (act[k]) {
+          if (p.bias) {
+            float f[8];
+            unpack8(r[k], f);
+            add_bias8(p, vs[k] * 8, f);
+            r[k] = pack8(f);
           }
+          multimem_st16((char*)p.mc_ptr + p.buf_off + vs[k] * 16, r[k]);
+        }
+    } else if (p.ws <= 4) {
+      U4 x[UNR][4];
 #pragma unroll
-        for (int s = 0; s < 8; ++s)
-          if (s0 + s < p.ws) acc8(x[s], f);
-      }
-      r = pack8(f);
-      for (int s = 0; s < p.ws; ++s) {
-        int peer = p.rank + s;
-        if (peer >= p.ws) peer -= p.ws;
-        st16(symm_buf(p, peer) + v * 16, r);
+      for (int k = 0; k < UNR; ++k)
+        if (act[k]) {
+#pragma unroll
+          for (int s = 0; s < 4; ++s)
+            if (s < p.ws) {
+              int peer = p.rank + s;
+              if (peer >= p.ws) peer -= p.ws;
+              x[k][s] = ld16(symm_buf(p, peer) + vs[k] * 16);
+            }
+        }
+#pragma unroll
+      for (int k = 0; k < UNR; ++k)
+        if (act[k]) {
+          float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (p.bias) add_bias8(p, vs[k] * 8, f);
+#pragma unroll
+          for (int s = 0; s < 4; ++s)
+            if (s < p.ws) acc8(x[k][s], f);
+          const U4 r = pack8(f);
+          for (int s = 0; s < p.ws; ++s) {
+            int peer = p.rank + s;
+            if (peer >= p.ws) peer -= p.ws;
+            st16(symm_buf(p, peer) + vs[k] * 16, r);
+          }
+        }
+    } else {
+#pragma unroll 1
+      for (int k = 0; k < UNR; ++k) {
+        if (!act[k]) continue;
+        const size_t v = vs[k];
+        float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (p.bias) add_bias8(p, v * 8, f);
+        U4 x[8];
+        for (int s0 = 0; s0 < p.ws; s0 += 8) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) {
+              int peer = p.rank + s0 + s;
+              if (peer >= p.ws) peer -= p.ws;
+              x[s] = ld16(symm_buf(p, peer) + v * 16);
+            }
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) acc8(x[s], f);
+        }
+        const U4 r = pack8(f);
+        for (int s = 0; s < p.ws; ++s) {
+          int peer = p.rank + s;
+          if (peer >= p.ws) peer -= p.ws;
+          st16(symm_buf(p, peer) + v * 16, r);
+        }
       }
     }
   }

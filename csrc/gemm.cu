@@ -6,9 +6,10 @@
 //    consume remote chunks as their flags appear. One launch, no copy engine, no second stream.
 //  * GEMM -> reduce-scatter (reference: kraken/fused/gemm_reduce_scatter_fused.py:152-235 and
 //    gemm_reduce_scatter_ce_persistent.py:326-375): the epilogue pushes each finished tile straight
-//    into the OWNER rank's staging slab over NVLink and bumps a per-tile flag there; after its last
-//    GEMM tile every CTA turns reducer for tiles of its own slab, summing the ws slabs in fixed
-//    rank order (bitwise reproducible).
+//    into the OWNER rank's staging slab over NVLink and bumps a per-tile flag there. Every rank
+//    computes its own slab last; the epilogue of those tiles waits for the tile's flag, adds the
+//    peers' staged partial sums to the accumulator fragment in rank order (bitwise reproducible)
+//    and writes the final rows — there is no separate reduction pass.
 //  * GEMM -> all-reduce for decode (reference: kraken/fused/gemm_one_shot_all_reduce_fused.py:106-178):
 //    fp32 partial tile to the own staging buffer, per-tile flags to all peers, then each rank sums
 //    the tile from all ranks in rank order into its fp32 output.
@@ -25,6 +26,8 @@ namespace kraken {
 // ---------------------------------------------------------------------------------------------
 struct PlainHooks {
   int bn;
+  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
+  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
     return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols};
@@ -34,10 +37,13 @@ struct PlainHooks {
 
 struct AgHooks {
   int bn;
+  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
+  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   // Row tile tr covers gathered rows [tr*128, +128). Rows of the own shard come from the own
   // shard's tensor map at once; other rows wait until every chunk they touch has landed.
   __device__ __forceinline__ bool before_load(const GemmParams& p, int tr, const CUtensorMap*& rmap, int& row0) {
     const int lo = tr * kBM;
+    if (lo >= p.rows_r) return true;           // padding tile of a CTA pair: nothing to wait for
     const int hi = min(lo + kBM, p.rows_r) - 1;
     const int own_lo = p.rank * p.shard_rows;
     if (lo >= own_lo && hi < own_lo + p.shard_rows) {
@@ -60,27 +66,71 @@ struct AgHooks {
 struct RsHooks {
   int bn;
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
-  // Tile (tr, tc) of the full [M, N] product belongs to rank owner = row / slab_rows; it goes to
-  // slot `rank` of the owner's staging [ws][slab_rows][N].
+  __device__ __forceinline__ int owner_of(const GemmParams& p, int tr) const { return (tr * kBM) / p.slab_rows; }
+  __device__ __forceinline__ int local_tile(const GemmParams& p, int tr, int tc) const {
+    return (tr - owner_of(p, tr) * (p.slab_rows / kBM)) * p.tiles_c + tc;
+  }
+  // Own-slab tiles are computed last; by then the peers (which computed this slab earlier in their
+  // own order) have pushed their partial tiles. Wait for all ws-1 of them, then consume the flag.
+  __device__ __forceinline__ bool begin_tile(const GemmParams& p, int tr, int tc, int q, int lane) {
+    if (owner_of(p, tr) != p.rank || p.ws == 1) return true;
+    uint32_t* f = p.pads[p.rank] + p.flag_base + local_tile(p, tr, tc);
+    const uint32_t need = (uint32_t)(p.ws - 1);
+    if (lane == 0)
+      spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 55, 0, blockIdx.x));
+    __syncwarp();
+    epi_bar_sync();                       // every epilogue warp has seen the flag
+    if (q == 0 && lane == 0) red_add_relaxed_sys(f, 0u - need);
+    return status_ok(p.sync);
+  }
+  // Remote tiles go to slot `rank` of the owner's staging [ws][slab_rows][N]; own tiles go to `out`.
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    const int owner = (tr * kBM) / p.slab_rows;
+    const int owner = owner_of(p, tr);
+    const int row0 = tr * kBM - owner * p.slab_rows;
+    if (owner == p.rank) return TileDest{(char*)p.out, p.ldo, row0, tc * bn, p.slab_rows, p.rows_c};
     char* base = (char*)p.bufs[owner] + (size_t)p.rank * p.slab_rows * p.rows_c * 2;
-    return TileDest{base, (long long)p.rows_c, tr * kBM - owner * p.slab_rows, tc * bn, p.slab_rows, p.rows_c};
+    return TileDest{base, (long long)p.rows_c, row0, tc * bn, p.slab_rows, p.rows_c};
+  }
+  // Own tiles: add the peers' staged partial sums (bf16) to the fp32 fragment, in rank order.
+  __device__ __forceinline__ void add_to_chunk(const GemmParams& p, int tr, int tc, int row_in_tile, int col_in_tile,
+                                               uint32_t (&r)[32], int n) {
+    if (owner_of(p, tr) != p.rank || p.ws == 1) return;
+    const int row = tr * kBM - p.rank * p.slab_rows + row_in_tile;
+    const int col = tc * bn + col_in_tile;
+    if (row >= p.slab_rows) return;
+    const char* stage = (const char*)p.bufs[p.rank];
+    const size_t slab_bytes = (size_t)p.slab_rows * p.rows_c * 2;
+    const size_t off = ((size_t)row * p.rows_c + col) * 2;
+    for (int s = 0; s < p.ws; ++s) {
+      if (s == p.rank) continue;
+      const char* src = stage + (size_t)s * slab_bytes + off;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (u * 8 < n && col + u * 8 < p.rows_c) {      // N % 8 == 0: a 16-byte unit is in or out as a whole
+          const U4 v = ld16(src + u * 16);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            r[u * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e]) + bf16lo(w[e]));
+            r[u * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e + 1]) + bf16hi(w[e]));
+          }
+        }
+      }
+    }
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
+    const int owner = owner_of(p, tr);
+    if (owner == p.rank) return true;
     epi_bar_sync();   // all four epilogue warps have issued their stores of this tile
-    if (q == 0 && lane == 0) {
-      const int owner = (tr * kBM) / p.slab_rows;
-      const int tiles_per_slab = p.slab_rows / kBM;
-      const int local_tile = (tr - owner * tiles_per_slab) * p.tiles_c + tc;
-      red_add_release_sys(p.pads[owner] + p.flag_base + local_tile, 1u);
-    }
+    if (q == 0 && lane == 0) red_add_release_sys(p.pads[owner] + p.flag_base + local_tile(p, tr, tc), 1u);
     return true;
   }
 };
 
 struct ArHooks {
   int bn;
+  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
+  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   // partial tile -> own fp32 staging [out_rows][out_cols]
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
@@ -105,23 +155,51 @@ struct ArHooks {
     if (p.transposed) { r_lo = tc * bn; r_n = bn; c_lo = tr * kBM; c_n = kBM; }
     else { r_lo = tr * kBM; r_n = kBM; c_lo = tc * bn; c_n = bn; }
     const int upr = c_n / 4;   // 16-byte units per row
-    for (int i = tid; i < r_n * upr; i += 128) {
-      const int rr = r_lo + i / upr, cc = c_lo + (i % upr) * 4;
-      if (rr >= p.out_rows || cc >= p.out_cols) continue;
-      const size_t off = ((size_t)rr * p.out_cols + cc) * 4;
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (cc + 4 <= p.out_cols && (p.out_cols % 4) == 0 && (p.ldo % 4) == 0) {
-        for (int s = 0; s < p.ws; ++s) {
-          U4 v = ld16((const char*)p.bufs[s] + off);
-          a.x += __uint_as_float(v.x); a.y += __uint_as_float(v.y);
-          a.z += __uint_as_float(v.z); a.w += __uint_as_float(v.w);
+    const bool vec = (p.out_cols % 4) == 0 && (p.ldo % 4) == 0;
+    for (int i0 = tid; i0 < r_n * upr; i0 += 256) {
+      // two units per thread and all ranks' loads issued before the first add: the sum is bound
+      // by NVLink latency, so what counts is how many loads are in flight
+      size_t off[2];
+      int rr[2], cc[2];
+      bool act[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int i = i0 + 128 * k;
+        rr[k] = r_lo + i / upr;
+        cc[k] = c_lo + (i % upr) * 4;
+        act[k] = i < r_n * upr && rr[k] < p.out_rows && cc[k] < p.out_cols;
+        off[k] = ((size_t)rr[k] * p.out_cols + cc[k]) * 4;
+      }
+      if (vec) {
+        U4 x[2][8];
+        float4 a[2];
+        a[0] = a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < p.ws; s0 += 8) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (act[k] && s0 + s < p.ws) x[k][s] = ld16((const char*)p.bufs[s0 + s] + off[k]);
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (act[k] && s0 + s < p.ws) {
+                a[k].x += __uint_as_float(x[k][s].x); a[k].y += __uint_as_float(x[k][s].y);
+                a[k].z += __uint_as_float(x[k][s].z); a[k].w += __uint_as_float(x[k][s].w);
+              }
         }
-        *(float4*)((float*)p.out + (size_t)rr * p.ldo + cc) = a;
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+          if (act[k]) *(float4*)((float*)p.out + (size_t)rr[k] * p.ldo + cc[k]) = a[k];
       } else {
-        for (int e = 0; e < 4 && cc + e < p.out_cols; ++e) {
-          float acc = 0.f;
-          for (int s = 0; s < p.ws; ++s) acc += ((const volatile float*)((const char*)p.bufs[s] + off))[e];
-          ((float*)p.out)[(size_t)rr * p.ldo + cc + e] = acc;
+        for (int k = 0; k < 2; ++k) {
+          if (!act[k]) continue;
+          for (int e = 0; e < 4 && cc[k] + e < p.out_cols; ++e) {
+            float acc = 0.f;
+            for (int s = 0; s < p.ws; ++s) acc += ((const volatile float*)((const char*)p.bufs[s] + off[k]))[e];
+            ((float*)p.out)[(size_t)rr[k] * p.ldo + cc[k] + e] = acc;
+          }
         }
       }
     }
@@ -135,6 +213,8 @@ struct ArHooks {
 // slab's signal word to 1 with system-scope release, which a stream wait on the host side consumes.
 struct CeHooks {
   int bn;
+  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
+  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
     return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols};
@@ -226,49 +306,6 @@ __device__ __forceinline__ void ag_comm_cta(const GemmParams& p, unsigned comm_i
 }
 
 // ---------------------------------------------------------------------------------------------
-// RS reducer: after the GEMM loop, sum the ws staged slabs of my own slab tile by tile.
-// ---------------------------------------------------------------------------------------------
-template <int BN>
-__device__ __forceinline__ void rs_reduce_phase(const GemmParams& p, unsigned bid, unsigned nb) {
-  const int tiles_per_slab = p.slab_rows / kBM;
-  const int slab_tiles = tiles_per_slab * p.tiles_c;
-  const char* stage = (const char*)p.bufs[p.rank];
-  const size_t slab_bytes = (size_t)p.slab_rows * p.rows_c * 2;
-  // visit tiles in the order peers finish them: each peer computes my slab at a different time,
-  // but all of them sweep it row tile by row tile
-  for (int t = bid; t < slab_tiles; t += nb) {
-    uint32_t* f = p.pads[p.rank] + p.flag_base + t;
-    if (threadIdx.x == 0) {
-      const uint32_t need = (uint32_t)p.ws;
-      if (spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync,
-                     make_status(KR_ERR_TIMEOUT_SIGNAL, 55, 0, bid)))
-        red_add_relaxed_sys(f, 0u - need);
-    }
-    __syncthreads();
-    if (!status_ok(p.sync)) return;
-    const int tr = t / p.tiles_c, tc = t % p.tiles_c;
-    const int upr = BN / 8;   // 16-byte units per tile row
-    for (int i = threadIdx.x; i < kBM * upr; i += blockDim.x) {
-      const int rr = tr * kBM + i / upr;
-      const int cc = tc * BN + (i % upr) * 8;
-      if (rr >= p.slab_rows || cc >= p.rows_c) continue;
-      const size_t off = ((size_t)rr * p.rows_c + cc) * 2;
-      float f8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      U4 x[8];
-      for (int s0 = 0; s0 < p.ws; s0 += 8) {
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          if (s0 + s < p.ws) x[s] = ld16(stage + (size_t)(s0 + s) * slab_bytes + off);
-#pragma unroll
-        for (int s = 0; s < 8; ++s)
-          if (s0 + s < p.ws) acc8(x[s], f8);
-      }
-      st16((char*)p.out + ((size_t)rr * p.ldo + cc) * 2, pack8(f8));
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // kernels
 // ---------------------------------------------------------------------------------------------
 template <int BN>
@@ -288,8 +325,6 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
   } else if (p.mode == GEMM_RS) {
     RsHooks h{BN};
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
-    __syncthreads();
-    rs_reduce_phase<BN>(p, bid, nb);
     // staging slabs and flags may be reused by the next launch only after every rank is done
     symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
   } else if (p.mode == GEMM_CE) {
@@ -300,6 +335,34 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
     symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 57);
   }
+}
+
+// CTA-pair kernel (256 x 256 tiles, tcgen05 cta_group::2); launched as clusters of two CTAs.
+__device__ __forceinline__ void gemm_pair_body(const GemmParams& p, unsigned bid, unsigned nb) {
+  extern __shared__ unsigned char smem_raw[];
+  const unsigned n_mma = (unsigned)p.num_mma_ctas;   // even
+  if (p.mode == GEMM_PLAIN) {
+    PlainHooks h{256};
+    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
+  } else if (p.mode == GEMM_AG) {
+    if (bid >= n_mma) {
+      ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+    } else {
+      AgHooks h{256};
+      gemm_mainloop_pair(p, bid / 2, n_mma / 2, h, smem_raw);
+    }
+  } else if (p.mode == GEMM_RS) {
+    RsHooks h{256};
+    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
+    symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
+  } else {
+    CeHooks h{256};
+    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
+  }
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_pair_kernel(const __grid_constant__ GemmParams p) {
+  gemm_pair_body(p, blockIdx.x, gridDim.x);
 }
 
 #define KR_DEFINE_GEMM(BN)                                                                              \
@@ -365,6 +428,19 @@ static int get_tmap(const void* ptr, unsigned long long rows, unsigned long long
   return KR_SUCCESS;
 }
 
+// Row tiles (of 128 rows) that share one sweep over the column tiles. Larger groups re-read the
+// column operand from DRAM fewer times; the group's rows (group * 128 * K * 2 bytes) should stay
+// well inside the 126 MB L2. KRAKEN_GEMM_GROUP overrides for tuning.
+static int default_group_r() {
+  static int v = 0;
+  if (v == 0) {
+    const char* e = getenv("KRAKEN_GEMM_GROUP");
+    v = e ? atoi(e) : 16;
+    if (v < 1) v = 16;
+  }
+  return v;
+}
+
 static int pick_bn(int rows_c) {
   if (rows_c > 128) return 256;
   if (rows_c > 64) return 128;
@@ -375,6 +451,57 @@ static int pick_bn(int rows_c) {
 
 constexpr size_t kAgSmem = (size_t)kAgSlots * kAgPiece + 1024 + 128;
 static_assert(kAgSmem <= (size_t)kSmemLimit, "comm ring exceeds shared memory");
+
+static bool pair_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KRAKEN_GEMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// Whether this problem can run on the CTA-pair kernel: 256-column tiles, at least one full pair of
+// row tiles, a mode the pair kernel implements, slabs aligned to 256 rows where tiles belong to
+// ranks, and no rank emulation (the emulated launch is cooperative, not clustered).
+static bool pair_eligible(int bn, const GemmParams& p) {
+  if (!pair_enabled() || emu_recorder().active) return false;
+  if (bn != 256 || p.transposed || p.rows_r < 256) return false;
+  if (p.mode == GEMM_AR) return false;
+  if ((p.mode == GEMM_RS || p.mode == GEMM_CE) && (p.slab_rows % 256) != 0) return false;
+  return true;
+}
+
+// Re-expresses the tiling in 256-row pair tiles and launches clusters of two CTAs.
+// nb_single = CTAs the single-CTA kernel would have used (already capped); n_comm = comm CTAs (AG).
+static int launch_pair(GemmParams p, unsigned cap, unsigned n_comm, cudaStream_t stream) {
+  const int tiles128 = p.tiles_r;
+  p.tiles_r = (p.rows_r + 255) / 256;
+  p.pivot_r = p.tiles_r > 0 ? (p.pivot_r / 2) % p.tiles_r : 0;
+  p.group_r = p.group_r >= 2 ? p.group_r / 2 : 1;
+  if (p.mode == GEMM_RS || p.mode == GEMM_CE) {
+    const int per_slab = p.slab_rows / 256;
+    if (p.group_r > per_slab) p.group_r = per_slab;
+    while (per_slab % p.group_r) --p.group_r;
+  }
+  (void)tiles128;
+  // each CTA of a pair loads its own 128 rows of the column operand: box of 128 rows, not 256
+  int rc0 = get_tmap(p.host_c_ptr, p.rows_c, p.K, p.host_ldc, 128, &p.tmap_c);
+  if (rc0) return rc0;
+  n_comm = (n_comm + 1) & ~1u;
+  cap &= ~1u;
+  unsigned n_mma = 2u * (unsigned)(p.tiles_r * p.tiles_c);
+  if (n_mma > cap - n_comm) n_mma = (cap - n_comm) & ~1u;
+  if (n_mma < 2) return fail(KR_FAIL_ARG, "not enough CTAs for the pair kernel");
+  p.num_mma_ctas = (int)n_mma;
+  size_t smem = PairCfg::SMEM;
+  if (p.mode == GEMM_AG && smem < kAgSmem) smem = kAgSmem;
+  int rc = ensure_dynamic_smem((const void*)gemm_pair_kernel, smem);
+  if (rc) return rc;
+  void* args[] = {(void*)&p};
+  KR_CUDA(cudaLaunchKernel((const void*)gemm_pair_kernel, dim3(n_mma + n_comm), dim3(kGemmThreads), args, smem, stream));
+  return KR_SUCCESS;
+}
 
 static int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream) {
   const size_t floor_smem = p.mode == GEMM_AG ? kAgSmem : 0;   // comm CTAs reuse the block's shared memory
@@ -412,13 +539,15 @@ static int setup_problem(GemmParams& p, const void* a, long long lda, const void
   *bn_out = bn;
   p.tiles_r = (p.rows_r + kBM - 1) / kBM;
   p.tiles_c = (p.rows_c + bn - 1) / bn;
-  p.group_r = 8;
+  p.group_r = default_group_r();
   p.pivot_r = 0;
   p.transposed = swap ? 1 : 0;
   int rc = get_tmap(r, p.rows_r, K, ldr, kBM, &p.tmap_r);
   if (rc) return rc;
   rc = get_tmap(c, p.rows_c, K, ldc, bn, &p.tmap_c);
   if (rc) return rc;
+  p.host_c_ptr = c;
+  p.host_ldc = ldc;
   p.tmap_r_local = p.tmap_r;
   return KR_SUCCESS;
 }
@@ -436,8 +565,10 @@ KR_API int kr_tmap_cache_stats(unsigned long long* hits, unsigned long long* mis
 
 // out[M,N] (bf16 or fp32, row stride ldo) = a[M,K] (row stride lda) * bt[N,K]^T (row stride ldb).
 // swap_ab: -1 auto (weights on the 128-row side when M <= 64), 0/1 forced.
+// use_pair: 0 forces the single-CTA kernel, anything else lets eligible shapes use CTA pairs.
 KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long ldb, void* out, long long ldo, int M,
-                        int N, int K, int out_fp32, int swap_ab, int bn_override, int max_ctas, cudaStream_t stream) {
+                        int N, int K, int out_fp32, int swap_ab, int bn_override, int max_ctas, int use_pair,
+                        cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   GemmParams p;
@@ -457,6 +588,7 @@ KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long 
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
   unsigned cap = grid_cap(d);
   if (max_ctas > 0 && (unsigned)max_ctas < cap) cap = (unsigned)max_ctas;
+  if (pair_eligible(bn, p) && cap >= 2 && use_pair != 0) return launch_pair(p, cap, 0, stream);
   if (nb > cap) nb = cap;
   p.num_mma_ctas = (int)nb;
   return launch_gemm(bn, p, nb, stream);
@@ -512,6 +644,7 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   unsigned n_comm = num_comm_ctas > 0 ? (unsigned)num_comm_ctas : (num_comm_ctas < 0 ? 0u : 8u);
   if (n_comm >= cap) n_comm = cap > 1 ? cap / 2 : 1;
   KR_REQUIRE(cap >= 2, "all-gather GEMM needs at least two CTAs");
+  if (pair_eligible(bn, p) && cap >= 4) return launch_pair(p, cap, n_comm, stream);
   unsigned n_mma = (unsigned)(p.tiles_r * p.tiles_c);
   if (n_mma > cap - n_comm) n_mma = cap - n_comm;
   p.num_mma_ctas = (int)n_mma;
@@ -557,7 +690,8 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, uint32_t* const* pads, int rank, i
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
   unsigned cap = grid_cap(d);
   if (nb > cap) nb = cap;
-  KR_REQUIRE((unsigned long long)pad_base + (unsigned long long)nb * ws <= flag_base, "barrier slots overlap tile flags");
+  KR_REQUIRE((unsigned long long)pad_base + (unsigned long long)cap * ws <= flag_base, "barrier slots overlap tile flags");
+  if (pair_eligible(bn, p) && cap >= 2) return launch_pair(p, cap, 0, stream);
   p.num_mma_ctas = (int)nb;
   return launch_gemm(bn, p, nb, stream);
 }
@@ -632,6 +766,7 @@ KR_API int kr_gemm_ce_producer_bf16(const void* a, long long lda, const void* bt
   p.sync = sync_ctx(d);
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
   unsigned cap = grid_cap(d);
+  if (pair_eligible(bn, p) && cap >= 2) return launch_pair(p, cap, 0, stream);
   if (nb > cap) nb = cap;
   p.num_mma_ctas = (int)nb;
   return launch_gemm(bn, p, nb, stream);

@@ -74,6 +74,10 @@ struct alignas(64) GemmParams {
   // RS
   int slab_rows;             // M / ws
   SyncCtx sync;
+  // host-side bookkeeping (not read on the device): the column operand as given, so that a
+  // launcher can re-encode its tensor map with another box height
+  const void* host_c_ptr;
+  long long host_ldc;
 };
 
 // Linear persistent tile index -> (row tile, column tile): row tiles advance in groups of
@@ -96,13 +100,132 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 // Hooks a fused kernel supplies to the main loop.
 //   Producer hook: called by the producer lane before loading row tile `tr`; returns the tensor
 //   map to read it from and may rewrite the row coordinate; false aborts.
-//   Epilogue hook: decides where tile (tr, tc) is stored and what happens once it is stored.
+//   Epilogue hooks: begin_tile (may wait for peers' data), tile_dest (where tile (tr, tc) is
+//   stored), add_to_chunk (adds other ranks' partial sums to a row fragment still in registers;
+//   row-major path only), after_store (what happens once the tile is stored).
 struct TileDest {
   char* base;        // address of element (0,0) of the destination matrix
   long long ld;      // elements per destination row
   int row0, col0;    // where the tile's (0,0) lands in the destination
   int rows, cols;    // destination bounds
 };
+
+// Epilogue of one tile, run by the four epilogue warps: TMEM -> registers -> (hook: add peers'
+// partial sums) -> convert -> swizzled staging in shared memory -> coalesced global stores.
+// `tempty_addr` is the mbarrier that returns the accumulator to the MMA issuer: a local barrier,
+// or (PAIR) the shared::cluster address of the barrier in the pair's leader CTA.
+template <int BN, bool PAIR, class Hooks>
+__device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& hooks, int tr, int tc, int acc,
+                                                   uint32_t tmem_base, int q, int lane, unsigned char* stg,
+                                                   uint32_t tempty_addr) {
+  if (!hooks.begin_tile(p, tr, tc, q, lane)) return false;
+  TileDest dst = hooks.tile_dest(p, tr, tc);
+  const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+  if (p.transposed) {
+    // D(i, j) -> dst[col0 + j][row0 + i]: lanes = consecutive destination columns.
+    const int dcol = dst.row0 + q * 32 + lane;     // destination column index (tile row i)
+    constexpr int CH = BN < 32 ? BN : 32;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += CH) {
+      uint32_t r[32];
+      if (CH == 32) tmem_ld32(t_addr + c0, r);
+      else tmem_ld16(t_addr + c0, r);
+      tmem_ld_wait();
+      if (c0 + CH >= BN) {
+        // all TMEM reads of this accumulator are done: hand it back before the global stores
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { if (PAIR) mbar_arrive_cluster(tempty_addr); else mbar_arrive(tempty_addr); }
+      }
+      if (dcol < dst.cols) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int drow = dst.col0 + c0 + j;
+          if (drow < dst.rows) {
+            if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
+            else ((__nv_bfloat16*)dst.base)[(long long)drow * dst.ld + dcol] = __float2bfloat16(__uint_as_float(r[j]));
+          }
+        }
+      }
+    }
+  } else {
+    // Row-major store through per-warp staging: 32 rows x 256 bytes, 16-byte units XOR-swizzled
+    // by row so that both the row-per-lane writes and the row-contiguous reads are conflict-free.
+    const int elt = p.out_fp32 ? 4 : 2;
+    const int cols_per_pass = 256 / elt;               // 128 bf16 or 64 fp32 columns
+    const int passes = (BN + cols_per_pass - 1) / cols_per_pass;
+    const int pass_cols = BN < cols_per_pass ? BN : cols_per_pass;
+    const int units_per_row = pass_cols * elt / 16;    // 16-byte units actually used per row
+    const bool vec_ok = ((dst.ld * elt) % 16 == 0) && ((((uintptr_t)dst.base) & 15) == 0) && ((dst.col0 * elt) % 16 == 0);
+    for (int ps = 0; ps < passes; ++ps) {
+      constexpr int CH = BN < 32 ? BN : 32;
+      const int nch = pass_cols / CH;
+      for (int c = 0; c < nch; ++c) {
+        uint32_t r[32];
+        const int col = ps * cols_per_pass + c * CH;
+        if (CH == 32) tmem_ld32(t_addr + col, r);
+        else tmem_ld16(t_addr + col, r);
+        tmem_ld_wait();
+        if (ps == passes - 1 && c == nch - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { if (PAIR) mbar_arrive_cluster(tempty_addr); else mbar_arrive(tempty_addr); }
+        }
+        hooks.add_to_chunk(p, tr, tc, q * 32 + lane, col, r, CH);
+        if (p.out_fp32) {
+#pragma unroll
+          for (int u = 0; u < CH / 4; ++u) {
+            const int unit = c * (CH / 4) + u;
+            const int phys = (unit & 8) | ((unit ^ lane) & 7);
+            *(U4*)(stg + lane * 256 + phys * 16) = U4{r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]};
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < CH / 8; ++u) {
+            const int unit = c * (CH / 8) + u;
+            const int phys = (unit & 8) | ((unit ^ lane) & 7);
+            U4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+            *(U4*)(stg + lane * 256 + phys * 16) = v;
+          }
+        }
+      }
+      __syncwarp();
+      // coalesced write-out: `rpi` rows per warp instruction
+      const int rpi = 32 / units_per_row > 0 ? 32 / units_per_row : 1;
+      const int unit = lane % units_per_row;
+      const int rsub = lane / units_per_row;
+      const int per_unit = 16 / elt;
+      const int gcol = dst.col0 + ps * cols_per_pass + unit * per_unit;
+      if (rsub < rpi) {
+        for (int r0 = 0; r0 < 32; r0 += rpi) {
+          const int rr = r0 + rsub;
+          const int grow = dst.row0 + q * 32 + rr;
+          const int phys = (unit & 8) | ((unit ^ rr) & 7);
+          const U4 v = *(const U4*)(stg + rr * 256 + phys * 16);
+          if (grow < dst.rows) {
+            char* gp = dst.base + ((long long)grow * dst.ld + gcol) * elt;
+            if (vec_ok && gcol + per_unit <= dst.cols) {
+              st16(gp, v);
+            } else {
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+              for (int e = 0; e < per_unit; ++e)
+                if (gcol + e < dst.cols) {
+                  if (p.out_fp32) ((uint32_t*)gp)[e] = w[e];
+                  else ((uint16_t*)gp)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+                }
+            }
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
+  return hooks.after_store(p, tr, tc, q, lane);
+}
 
 template <int BN, class Hooks>
 __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid, unsigned nb, Hooks& hooks,
@@ -216,111 +339,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      TileDest dst = hooks.tile_dest(p, tr, tc);
-      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
-      if (p.transposed) {
-        // D(i, j) -> dst[col0 + j][row0 + i]: lanes = consecutive destination columns.
-        const int dcol = dst.row0 + q * 32 + lane;     // destination column index (tile row i)
-        constexpr int CH = BN < 32 ? BN : 32;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CH) {
-          uint32_t r[32];
-          if (CH == 32) tmem_ld32(t_addr + c0, r);
-          else tmem_ld16(t_addr + c0, r);
-          tmem_ld_wait();
-          if (c0 + CH >= BN) {
-            // all TMEM reads of this accumulator are done: hand it back before the global stores
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar(acc));
-          }
-          if (dcol < dst.cols) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int drow = dst.col0 + c0 + j;
-              if (drow < dst.rows) {
-                if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
-                else ((__nv_bfloat16*)dst.base)[(long long)drow * dst.ld + dcol] = __float2bfloat16(__uint_as_float(r[j]));
-              }
-            }
-          }
-        }
-      } else {
-        // Row-major store through per-warp staging: 32 rows x 256 bytes, 16-byte units XOR-swizzled
-        // by row so that both the row-per-lane writes and the row-contiguous reads are conflict-free.
-        const int elt = p.out_fp32 ? 4 : 2;
-        const int cols_per_pass = 256 / elt;               // 128 bf16 or 64 fp32 columns
-        const int passes = (BN + cols_per_pass - 1) / cols_per_pass;
-        const int pass_cols = BN < cols_per_pass ? BN : cols_per_pass;
-        const int units_per_row = pass_cols * elt / 16;    // 16-byte units actually used per row
-        const bool vec_ok = ((dst.ld * elt) % 16 == 0) && ((((uintptr_t)dst.base) & 15) == 0) && ((dst.col0 * elt) % 16 == 0);
-        for (int ps = 0; ps < passes; ++ps) {
-          constexpr int CH = BN < 32 ? BN : 32;
-          const int nch = pass_cols / CH;
-          for (int c = 0; c < nch; ++c) {
-            uint32_t r[32];
-            const int col = ps * cols_per_pass + c * CH;
-            if (CH == 32) tmem_ld32(t_addr + col, r);
-            else tmem_ld16(t_addr + col, r);
-            tmem_ld_wait();
-            if (ps == passes - 1 && c == nch - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(acc));
-            }
-            if (p.out_fp32) {
-#pragma unroll
-              for (int u = 0; u < CH / 4; ++u) {
-                const int unit = c * (CH / 4) + u;
-                const int phys = (unit & 8) | ((unit ^ lane) & 7);
-                *(U4*)(stg + lane * 256 + phys * 16) = U4{r[4 * u], r[4 * u + 1], r[4 * u + 2], r[4 * u + 3]};
-              }
-            } else {
-#pragma unroll
-              for (int u = 0; u < CH / 8; ++u) {
-                const int unit = c * (CH / 8) + u;
-                const int phys = (unit & 8) | ((unit ^ lane) & 7);
-                U4 v;
-                v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
-                v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
-                v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
-                v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
-                *(U4*)(stg + lane * 256 + phys * 16) = v;
-              }
-            }
-          }
-          __syncwarp();
-          // coalesced write-out: `rpi` rows per warp instruction
-          const int rpi = 32 / units_per_row > 0 ? 32 / units_per_row : 1;
-          const int unit = lane % units_per_row;
-          const int rsub = lane / units_per_row;
-          const int per_unit = 16 / elt;
-          const int gcol = dst.col0 + ps * cols_per_pass + unit * per_unit;
-          if (rsub < rpi) {
-            for (int r0 = 0; r0 < 32; r0 += rpi) {
-              const int rr = r0 + rsub;
-              const int grow = dst.row0 + q * 32 + rr;
-              const int phys = (unit & 8) | ((unit ^ rr) & 7);
-              const U4 v = *(const U4*)(stg + rr * 256 + phys * 16);
-              if (grow < dst.rows) {
-                char* gp = dst.base + ((long long)grow * dst.ld + gcol) * elt;
-                if (vec_ok && gcol + per_unit <= dst.cols) {
-                  st16(gp, v);
-                } else {
-                  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-                  for (int e = 0; e < per_unit; ++e)
-                    if (gcol + e < dst.cols) {
-                      if (p.out_fp32) ((uint32_t*)gp)[e] = w[e];
-                      else ((uint16_t*)gp)[e] = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
-                    }
-                }
-              }
-            }
-          }
-          __syncwarp();
-        }
-      }
-      ok = hooks.after_store(p, tr, tc, q, lane);
+      ok = gemm_epilogue_tile<BN, false>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, tempty_bar(acc));
     }
   }
 
@@ -330,6 +349,173 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a 2-CTA cluster compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2. Each CTA TMA-loads (plain, non-multicast loads) its own 128 rows of the
+// row operand and its own 128 rows of the column operand, so every stage moves 32 KB per CTA
+// instead of 48 KB and six stages fit; the leader CTA (cluster rank 0) issues the MMAs, which
+// read both CTAs' shared memory; each CTA keeps the accumulator rows of its own 128 rows in its
+// own TMEM and runs the same epilogue as the single-CTA kernel on them.
+//   full[s]    in the leader, 1 arrival (the leader's expect_tx for both CTAs' bytes) + the bytes
+//   empty[s]   one per CTA, 1 arrival: the leader commits to its own and to the peer's barrier
+//   tfull[a]   one per CTA, 1 arrival: same double commit
+//   tempty[a]  in the leader, 8 arrivals: the four epilogue warps of each CTA
+// ---------------------------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;                 // pair tile: 256 rows x 256 columns
+  static constexpr int A_BYTES = kBM * kBK * 2;  // this CTA's 128 rows of the row operand
+  static constexpr int B_BYTES = 128 * kBK * 2;  // this CTA's 128 rows of the column operand
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int EPI = 4 * kEpiWarpBytes;
+  static constexpr int STAGES = 6;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM = 1024 + STAGES * STAGE + EPI + 512;
+};
+static_assert(PairCfg::SMEM <= kSmemLimit, "pair kernel shared memory");
+
+template <class Hooks>
+__device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned pair_id, unsigned num_pairs,
+                                                   Hooks& hooks, unsigned char* smem_raw) {
+  using Cfg = PairCfg;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t stage0 = smem_base;
+  unsigned char* epi_ptr = smem_al + Cfg::STAGES * Cfg::STAGE;
+  const uint32_t bars = smem_base + Cfg::STAGES * Cfg::STAGE + Cfg::EPI;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * Cfg::STAGES + 2 + a); };
+  uint32_t* tmem_slot = (uint32_t*)(smem_al + Cfg::STAGES * Cfg::STAGE + Cfg::EPI + 8 * (2 * Cfg::STAGES + 4));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.tiles_r * p.tiles_c;      // tiles_r counts 256-row pair tiles here
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    // ================= TMA producer (both CTAs) =================
+    if (elect_one()) {
+      tma_prefetch_desc(&p.tmap_r);
+      tma_prefetch_desc(&p.tmap_c);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+        int tr2, tc;
+        tile_coords(p, t, tr2, tc);
+        const int tr = 2 * tr2 + (int)cta;
+        const CUtensorMap* rmap = &p.tmap_r;
+        int row0 = tr * kBM;
+        ok = hooks.before_load(p, tr, rmap, row0);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, p.sync, 44);
+          if (!ok) break;
+          const uint32_t lead_full = mapa_shared(full_bar(s), 0);
+          // Only the leader arrives (with the byte count of BOTH CTAs); the peer's loads just
+          // complete bytes on the leader's barrier. The peer cannot run a phase ahead: it waits for
+          // its own empty barrier, which the leader signals after the MMAs that waited on full[s].
+          if (leader) mbar_expect_tx(full_bar(s), 2 * (Cfg::A_BYTES + Cfg::B_BYTES));
+          const uint32_t sa = stage0 + s * Cfg::STAGE;
+          tma_load_2d_pair(sa, rmap, lead_full, kb * kBK, row0);
+          tma_load_2d_pair(sa + Cfg::A_BYTES, &p.tmap_c, lead_full, kb * kBK, tc * Cfg::BN + (int)cta * 128);
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer (leader CTA only) =================
+    if (leader && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, Cfg::BN);
+      uint32_t peer_empty[Cfg::STAGES], peer_tfull[2];
+      for (int s = 0; s < Cfg::STAGES; ++s) peer_empty[s] = mapa_shared(empty_bar(s), 1);
+      for (int a = 0; a < 2; ++a) peer_tfull[a] = mapa_shared(tfull_bar(a), 1);
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+        ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, p.sync, 45);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full_bar(s), ph, p.sync, 46);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = stage0 + s * Cfg::STAGE;
+          const uint64_t adesc = make_smem_desc_sw128(sa);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k)
+            umma_bf16_pair(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(s));      // own stage free
+          umma_commit_pair(peer_empty[s]);     // peer's stage free
+          if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (ok) {
+          umma_commit_pair(tfull_bar(acc));
+          umma_commit_pair(peer_tfull[acc]);
+        }
+      }
+    }
+  } else {
+    // ================= epilogue warps (both CTAs, own 128 rows) =================
+    const int q = warp & 3;
+    unsigned char* stg = epi_ptr + (warp - 2) * kEpiWarpBytes;
+    const uint32_t lead_tempty[2] = {mapa_shared(tempty_bar(0), 0), mapa_shared(tempty_bar(1), 0)};
+    int it = 0;
+    bool ok = true;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
+      int tr2, tc;
+      tile_coords(p, t, tr2, tc);
+      const int tr = 2 * tr2 + (int)cta;
+      const int acc = it & 1;
+      const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+      ok = mbar_wait(tfull_bar(acc), acc_ph, p.sync, 47);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      ok = gemm_epilogue_tile<Cfg::BN, true>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, lead_tempty[acc]);
+    }
+  }
+
+  // ---- teardown: nobody leaves while the pair may still touch its shared memory or barriers
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

@@ -140,10 +140,19 @@ __device__ void ar_norm_one_shot_body(const NormParams& p, unsigned bid, unsigne
 #pragma unroll
         for (int j = 0; j < 8; ++j) f[i][j] = 0.f;
         if (p.bias) norm_add_bias8(p, (size_t)r * p.D + (size_t)v * 8, f[i]);
-        for (int s = 0; s < p.ws; ++s) {
-          int peer = p.rank + s;
-          if (peer >= p.ws) peer -= p.ws;
-          acc8(ld16(symm_buf(p, peer) + off + (size_t)v * 16), f[i]);
+        // all peers' loads are issued before any is consumed: one NVLink latency, not ws of them
+        U4 x[8];
+        for (int s0 = 0; s0 < p.ws; s0 += 8) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) {
+              int peer = p.rank + s0 + s;
+              if (peer >= p.ws) peer -= p.ws;
+              x[s] = ld16(symm_buf(p, peer) + off + (size_t)v * 16);
+            }
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) acc8(x[s], f[i]);
         }
       }
     }
@@ -186,10 +195,18 @@ __device__ __forceinline__ void ar_norm_two_shot_impl(const NormParams& p, unsig
       } else {
         float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (p.bias) norm_add_bias8(p, (size_t)r * p.D + (size_t)v * 8, f);
-        for (int s = 0; s < p.ws; ++s) {
-          int peer = p.rank + s;
-          if (peer >= p.ws) peer -= p.ws;
-          acc8(ld16(symm_buf(p, peer) + off), f);
+        U4 x[8];
+        for (int s0 = 0; s0 < p.ws; s0 += 8) {
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) {
+              int peer = p.rank + s0 + s;
+              if (peer >= p.ws) peer -= p.ws;
+              x[s] = ld16(symm_buf(p, peer) + off);
+            }
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            if (s0 + s < p.ws) acc8(x[s], f);
         }
         out = pack8(f);
         for (int s = 0; s < p.ws; ++s) {
@@ -223,8 +240,10 @@ KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot_mc, NormParams, kNormMaxThreads)
 using namespace kraken;
 
 static unsigned norm_threads(int D) {
+  // one 16-byte vector per thread while the row fits a block: every load of a row is then in
+  // flight at once, which is what matters when the loads cross NVLink
   unsigned nvec = (unsigned)D / 8;
-  unsigned t = (nvec + kNormVpt - 1) / kNormVpt;
+  unsigned t = nvec;
   t = (t + 31) / 32 * 32;
   if (t < 64) t = 64;
   if (t > kNormMaxThreads) t = kNormMaxThreads;

@@ -24,9 +24,17 @@ namespace kraken {
 static std::mutex g_drv_mu;
 static std::map<std::string, void*> g_drv;
 
-void* driver_entry(const char* name) {
+void* driver_entry(const char* raw_name) {
+  // cuda.h renames some entry points with macros (cuStreamWriteValue32 -> cuStreamWriteValue32_v2);
+  // the runtime's lookup wants the base name and picks the version itself.
+  std::string base(raw_name);
+  for (const char* suffix : {"_v2", "_v3", "_ptsz"}) {
+    const size_t n = strlen(suffix);
+    if (base.size() > n && base.compare(base.size() - n, n, suffix) == 0) base.resize(base.size() - n);
+  }
+  const char* name = base.c_str();
   std::lock_guard<std::mutex> lk(g_drv_mu);
-  auto it = g_drv.find(name);
+  auto it = g_drv.find(base);
   if (it != g_drv.end()) return it->second;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
@@ -35,7 +43,7 @@ void* driver_entry(const char* name) {
     fn = nullptr;
     (void)cudaGetLastError();
   }
-  g_drv[name] = fn;
+  g_drv[base] = fn;
   return fn;
 }
 

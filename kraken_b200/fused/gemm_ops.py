@@ -24,7 +24,8 @@ from .gemm_common import as_k_major_a, as_k_major_bt
 def matmul(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, **kwargs) -> torch.Tensor:
     """Single-GPU C = A @ B on the library's tcgen05 kernel (bf16 inputs, fp32 accumulate).
     Not in the reference's API; it is the compute core of every fused op, exposed for tests and
-    roofline measurements. kwargs: swap_ab (-1 auto / 0 / 1), bn (column-tile override), max_ctas."""
+    roofline measurements. kwargs: swap_ab (-1 auto / 0 / 1), bn (column-tile override), max_ctas,
+    pair (0 forces the single-CTA kernel; default lets large shapes use CTA pairs)."""
     if a.device.type != "cuda":
         return ref.matmul_f32(a, b).to(out_dtype)
     a2, lda = as_k_major_a(a)
@@ -39,7 +40,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bflo
     _lib.check(_lib.lib().kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
                                        1 if out_dtype == torch.float32 else 0, int(kwargs.get("swap_ab", -1)),
                                        int(kwargs.get("bn", 0)), int(kwargs.get("max_ctas", 0)),
-                                       _lib.current_stream_ptr()))
+                                       int(kwargs.get("pair", 1)), _lib.current_stream_ptr()))
     return out
 
 
@@ -134,7 +135,7 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     L = _lib.lib()
     if info.world_size == 1:
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0,
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0, 1,
                                   _lib.current_stream_ptr()))
         return out
     hdl = symm_mem.get_symm_mem_workspace(group, M * N * 4, a.device)
@@ -166,7 +167,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
     L = _lib.lib()
     s = _lib.current_stream_ptr()
     if ws == 1:
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, s))
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, s))
     elif (M // ws) % 128 == 0 and N % 8 == 0:
         hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
         _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, hdl.rank, ws, a2.data_ptr(), lda,
@@ -177,7 +178,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
             raise ValueError("M * N must be a multiple of 8 * world size")
         hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
         stage = hdl.buffer_ptrs[hdl.rank]
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, s))
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, 1, s))
         _lib.check(L.kr_reduce_scatter(hdl.buffer_ptrs_dev, 0, hdl.signal_pad_ptrs_dev, hdl.rank, ws, None,
                                        out.data_ptr(), M * N, 0, 0, s))
     return out if out.dtype == a.dtype or a.dtype != torch.float32 else out.to(a.dtype)
@@ -209,7 +210,7 @@ def gemm_reduce_scatter_ce_persistent(a: torch.Tensor, b: torch.Tensor, reduce_o
     dev = a.device
     out = torch.empty((M // ws, N), dtype=torch.bfloat16, device=dev)
     if ws == 1:
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0,
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1,
                                   _lib.current_stream_ptr()))
         return out
     gemm_out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)

@@ -83,7 +83,7 @@ _PROTOS = {
     # gemm kernels
     "kr_tmap_cache_stats": (c_int, [POINTER(c_ulonglong), POINTER(c_ulonglong)]),
     "kr_gemm_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, _P]),
+                             c_int, c_int, _P]),
     "kr_ag_gemm_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int,
                                 c_int, _P, _P, c_int, c_uint32, _P]),
     "kr_gemm_rs_bf16": (c_int, [_P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,

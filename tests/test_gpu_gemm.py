@@ -32,6 +32,27 @@ def test_gemm_basic(M, N, K):
     _close(c, a.float() @ bt.float().t(), K)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 512), (4096, 2048, 1024), (1000, 520, 264), (8192, 4096, 512),
+                                   (300, 1032, 136)])
+def test_gemm_cta_pair_kernel_matches_single_cta_kernel(M, N, K):
+    # 256 x 256 tiles on CTA pairs (tcgen05 cta_group::2) against the single-CTA kernel and fp32 PyTorch
+    a, bt = _ab(M, N, K, seed=11)
+    ref = a.float() @ bt.float().t()
+    c_pair = fused.matmul(a, bt.t(), swap_ab=0, pair=1)
+    c_single = fused.matmul(a, bt.t(), swap_ab=0, pair=0)
+    _close(c_pair, ref, K)
+    _close(c_single, ref, K)
+    assert torch.equal(c_pair, c_single)      # same accumulation order per element
+
+
+def test_gemm_cta_pair_many_tiles_per_pair():
+    a, bt = _ab(2048, 2048, 256, seed=12)
+    c = fused.matmul(a, bt.t(), max_ctas=6, pair=1)       # 64 pair tiles over 3 pairs
+    _close(c, a.float() @ bt.float().t(), 256)
+    c32 = fused.matmul(a, bt.t(), out_dtype=torch.float32, pair=1)
+    torch.testing.assert_close(c32, a.float() @ bt.float().t(), atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("M,N,K", [(100, 200, 72), (129, 257, 136), (1000, 520, 264), (77, 1032, 8), (5, 8, 64)])
 def test_gemm_ragged_shapes(M, N, K):
     a, bt = _ab(M, N, K, seed=1)
