@@ -59,6 +59,23 @@ def _zero_counters(device: torch.device, n: int, emu) -> torch.Tensor:
     return t
 
 
+def _default_comm_ctas(n_local: int, ws: int) -> int:
+    """Comm CTAs of the fused all-gather GEMM. The first remote shard must land by the time the MMA
+    CTAs finish the local one, which needs M*K*2 bytes per GEMM time = (tensor rate) / N_local bytes
+    per second whatever the world size; one comm CTA sustains roughly 50 GB/s of bulk copies.
+    KRAKEN_NUM_COMM_SMS overrides."""
+    import os
+
+    if "KRAKEN_NUM_COMM_SMS" in os.environ:
+        return config.num_comm_sms()
+    if ws == 1:
+        return 2
+    rate = 1.45e15 / max(1, n_local)            # bytes per second needed
+    n = int(-(-rate // 50e9))
+    n = (n + 1) & ~1
+    return max(2, min(16, n))
+
+
 def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tensor | None = None,
                       progress: torch.Tensor | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
     """(gathered A [M, K], C [M, N] = gathered A @ b). `a_shared` is this rank's [M/ws, K] shard in
@@ -110,7 +127,7 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
                                      progress.data_ptr(), counters.data_ptr(), -1, 0, _lib.current_stream_ptr()))
         torch.cuda.current_stream().wait_stream(stream)
     else:
-        n_comm = int(kwargs.get("num_comm_sms", config.num_comm_sms()))
+        n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_comm_ctas(N, ws)
         _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
                                      a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
                                      progress.data_ptr(), counters.data_ptr(), n_comm, 0, _lib.current_stream_ptr()))
