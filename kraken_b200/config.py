@@ -8,7 +8,8 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_SIGNAL_PAD_BYTES`` signal-pad size of blocks from the native allocator (default 1 MiB)
 ``KRAKEN_FORCE_ALGO``       ``one_shot`` / ``two_shot`` / ``multimem``: overrides all-reduce selection
 ``KRAKEN_NUM_COMM_SMS``     comm CTAs of the fused all-gather GEMM (default 8)
-``KRAKEN_AG_MODE``          ``sm`` (in-kernel pull, default) or ``ce`` (copy engine + stream flags)
+``KRAKEN_AG_MODE``          ``ce`` (copy engines + stream flags feed the GEMM kernel, default) or ``sm`` (comm CTAs
+                            inside the GEMM kernel pull the shards)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
 ``BENCHMARK_ITERS``         overrides the iteration count of the timing harness
@@ -52,8 +53,8 @@ def num_comm_sms() -> int:
 
 
 def ag_mode() -> str:
-    v = os.environ.get("KRAKEN_AG_MODE", "sm").strip().lower()
-    return v if v in ("sm", "ce") else "sm"
+    v = os.environ.get("KRAKEN_AG_MODE", "ce").strip().lower()
+    return v if v in ("sm", "ce") else "ce"
 
 
 def dump_kernel() -> bool:

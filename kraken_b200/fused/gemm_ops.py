@@ -62,7 +62,8 @@ def _zero_counters(device: torch.device, n: int, emu) -> torch.Tensor:
 def _default_comm_ctas(n_local: int, ws: int) -> int:
     """Comm CTAs of the fused all-gather GEMM. The first remote shard must land by the time the MMA
     CTAs finish the local one, which needs M*K*2 bytes per GEMM time = (tensor rate) / N_local bytes
-    per second whatever the world size; one comm CTA sustains roughly 50 GB/s of bulk copies.
+    per second whatever the world size; one comm CTA was measured to pull about 15 GB/s over NVLink
+    (its copies in flight cover only a fraction of the link's latency-bandwidth product).
     KRAKEN_NUM_COMM_SMS overrides."""
     import os
 
@@ -71,18 +72,21 @@ def _default_comm_ctas(n_local: int, ws: int) -> int:
     if ws == 1:
         return 2
     rate = 1.45e15 / max(1, n_local)            # bytes per second needed
-    n = int(-(-rate // 50e9))
+    n = int(-(-rate // 15e9))
     n = (n + 1) & ~1
-    return max(2, min(16, n))
+    return max(2, min(32, n))
 
 
 def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tensor | None = None,
                       progress: torch.Tensor | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
     """(gathered A [M, K], C [M, N] = gathered A @ b). `a_shared` is this rank's [M/ws, K] shard in
-    symmetric memory. One kernel: comm CTAs pull the peers' shards chunk by chunk into `a_out` and
-    raise `progress` flags, MMA CTAs begin with the local shard and follow the flags.
-    kwargs: splits_per_rank=1, num_comm_sms, backend="sm"|"ce" (copy engine + stream flags as in
-    the reference), group."""
+    symmetric memory. The persistent tcgen05 GEMM starts on the local shard (rank pivot) and
+    consumes remote chunks as their `progress` flags appear. Two engines fill `a_out` and raise the
+    flags: backend="ce" (default) — copy engines on a backend stream, one stream memory operation
+    per chunk, no SM spent on communication (measured fastest: a remote pull needs megabytes in
+    flight to cover NVLink latency, which a handful of CTAs cannot hold); backend="sm" — comm CTAs
+    inside the same kernel launch pull the shards with bulk async copies (single launch, no second
+    stream). kwargs: splits_per_rank=1, num_comm_sms, backend, group."""
     group = kwargs.get("group")
     if a_shared.device.type != "cuda":
         a, c = ref.all_gather_matmul(a_shared, b, group)
