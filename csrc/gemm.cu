@@ -101,18 +101,34 @@ struct RsHooks {
     const char* stage = (const char*)p.bufs[p.rank];
     const size_t slab_bytes = (size_t)p.slab_rows * p.rows_c * 2;
     const size_t off = ((size_t)row * p.rows_c + col) * 2;
-    for (int s = 0; s < p.ws; ++s) {
-      if (s == p.rank) continue;
-      const char* src = stage + (size_t)s * slab_bytes + off;
+    // Peers in batches of four: the 16 loads of a batch are issued before the first add, so a chunk
+    // costs ceil((ws-1)/4) memory round trips instead of ws-1. The order of the adds stays rank order.
+    for (int s0 = 0; s0 < p.ws; s0 += 4) {
+      U4 x[4][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (u * 8 < n && col + u * 8 < p.rows_c) {      // N % 8 == 0: a 16-byte unit is in or out as a whole
-          const U4 v = ld16(src + u * 16);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        if (s < p.ws && s != p.rank) {
+          const char* src = stage + (size_t)s * slab_bytes + off;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            r[u * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e]) + bf16lo(w[e]));
-            r[u * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e + 1]) + bf16hi(w[e]));
+          for (int u = 0; u < 4; ++u)
+            if (u * 8 < n && col + u * 8 < p.rows_c) x[k][u] = ld16(src + u * 16);   // N % 8 == 0: units are all-in or all-out
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        if (s < p.ws && s != p.rank) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (u * 8 < n && col + u * 8 < p.rows_c) {
+              const uint32_t w[4] = {x[k][u].x, x[k][u].y, x[k][u].z, x[k][u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                r[u * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e]) + bf16lo(w[e]));
+                r[u * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e + 1]) + bf16hi(w[e]));
+              }
+            }
           }
         }
       }
@@ -636,7 +652,7 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   if (p.tiles_r > 0) p.pivot_r %= p.tiles_r;
   // group must not mix chunks of different arrival times more than necessary
   int tiles_per_chunk = p.chunk_rows / kBM;
-  p.group_r = tiles_per_chunk >= 8 ? 8 : (tiles_per_chunk >= 1 ? tiles_per_chunk : 1);
+  p.group_r = tiles_per_chunk >= default_group_r() ? default_group_r() : (tiles_per_chunk >= 1 ? tiles_per_chunk : 1);
   p.sync = sync_ctx(d);
   unsigned cap = grid_cap(d);
   // num_comm_ctas < 0: no comm CTAs — an external engine (copy engine + stream memory operations)
@@ -684,7 +700,7 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, uint32_t* const* pads, int rank, i
   KR_REQUIRE((unsigned long long)flag_base + (unsigned long long)tiles_per_slab * p.tiles_c <= pad_words,
              "signal pad too small for the tile flags");
   p.pivot_r = (((rank + 1) % ws) * tiles_per_slab) % p.tiles_r;   // next rank's slab first, own slab last
-  p.group_r = tiles_per_slab >= 8 ? 8 : tiles_per_slab;
+  p.group_r = tiles_per_slab >= default_group_r() ? default_group_r() : tiles_per_slab;
   while (tiles_per_slab % p.group_r) --p.group_r;                 // groups never straddle two slabs
   p.sync = sync_ctx(d);
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
@@ -761,7 +777,7 @@ KR_API int kr_gemm_ce_producer_bf16(const void* a, long long lda, const void* bt
   p.slab_rows = M / ws;
   const int tiles_per_slab = p.slab_rows / kBM;
   p.pivot_r = (((rank + 1) % ws) * tiles_per_slab) % p.tiles_r;
-  p.group_r = tiles_per_slab >= 8 ? 8 : tiles_per_slab;
+  p.group_r = tiles_per_slab >= default_group_r() ? default_group_r() : tiles_per_slab;
   while (tiles_per_slab % p.group_r) --p.group_r;
   p.sync = sync_ctx(d);
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);

@@ -25,8 +25,8 @@ NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-Xcompiler", "-fPIC",
     "-Xcompiler", "-fvisibility=hidden",
-    f"-I{CSRC / 'include'}",
 ]
+INCLUDE_FLAG = f"-I{CSRC / 'include'}"      # absolute path: kept out of the staleness digest
 
 
 def _nvcc() -> str:
@@ -58,8 +58,23 @@ def sources() -> list[Path]:
 
 
 def build(verbose: bool = False, force: bool = False) -> Path:
-    """Compiles what changed and links the shared library. Returns its path."""
+    """Compiles what changed and links the shared library. Returns its path. Safe to call from
+    several processes at once (ranks of one job): an exclusive file lock serialises them and the
+    library is replaced atomically, so nobody ever loads a half-written file."""
+    import fcntl
+
     OUT_DIR.mkdir(parents=True, exist_ok=True)
+    with open(OUT_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not is_stale():
+                return LIB_PATH
+            return _build_locked(verbose, force)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool, force: bool) -> Path:
     nvcc = _nvcc()
     headers = _headers_digest()
     jobs = []
@@ -75,7 +90,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
 
     def compile_one(job):
         src, obj, stamp, digest = job
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, INCLUDE_FLAG, "-c", str(src), "-o", str(obj)]
         if verbose:
             print(" ".join(cmd), file=sys.stderr)
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -87,12 +102,14 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(compile_one, jobs))
     if jobs or not LIB_PATH.exists():
-        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objects), "-Xcompiler", "-fPIC", "-lpthread"]
+        tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
+        cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objects), "-Xcompiler", "-fPIC", "-lpthread"]
         if verbose:
             print(" ".join(cmd), file=sys.stderr)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 
