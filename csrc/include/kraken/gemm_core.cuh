@@ -71,6 +71,13 @@ struct alignas(64) GemmParams {
   uint32_t* progress;        // [ws * splits] chunk flags
   uint32_t* counters;        // [ws * splits] arrival counters (zeroed, self-resetting)
   int splits, shard_rows, chunk_rows;
+  // AR (decode): byte offsets inside every rank's staging buffer and the second flag bank
+  int ar_algo;               // 0: one-shot pull, 1: two-shot (tile owner reduces and publishes)
+  unsigned long long stage_off;   // one-shot: this call's staging (alternates between two halves)
+  unsigned long long part_off;    // two-shot: per-source partial tiles [ws][M][N] fp32
+  unsigned long long res_off;     // two-shot: reduced result [M][N] fp32
+  uint32_t flag2_base;            // two-shot: "result published" flags
+  void* mc_ptr;                   // multicast address of the staging buffer (NVLS) or nullptr
   // RS
   int slab_rows;             // M / ws
   SyncCtx sync;

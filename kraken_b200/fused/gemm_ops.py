@@ -139,10 +139,13 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
 
 
 def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
-    """fp32 [M, N] = all_reduce(a @ b): each rank holds a K-shard of both operands. The fp32
-    partial tile goes to the rank's symmetric staging buffer, per-tile flags replace a grid-wide
-    barrier, and every rank sums each tile from all ranks in rank order (identical results on all
-    ranks). Decode-sized M puts the weights on the 128-row side of the MMA."""
+    """fp32 [M, N] = all_reduce(a @ b): each rank holds a K-shard of both operands. One kernel:
+    the GEMM epilogue exchanges fp32 partial tiles behind per-tile flags (no grid-wide barrier).
+    Small outputs use the one-shot form (every rank sums the tile from all ranks, in the NVSwitch
+    when the staging buffer has a multicast mapping); larger ones the two-shot form (tile owner
+    t % ws receives all partials, sums them in rank order and publishes the result), which moves
+    ws/2 times fewer bytes. Every rank gets identical bits. Decode-sized M puts the weights on the
+    128-row side of the MMA. kwargs: group, swap_ab, algo="one_shot"|"two_shot"."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_all_reduce(a, b, group)
@@ -159,10 +162,16 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0, 1,
                                   _lib.current_stream_ptr()))
         return out
-    hdl = symm_mem.get_symm_mem_workspace(group, M * N * 4, a.device)
-    _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, a2.data_ptr(),
-                                 lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, int(kwargs.get("swap_ab", -1)),
-                                 0, config.TILE_FLAG_BASE, hdl.signal_pad_words, _lib.current_stream_ptr()))
+    need = 2 * (info.world_size + 1) * M * N * 4
+    hdl = symm_mem.get_symm_mem_workspace(group, need, a.device, kind="gemm_ar")
+    calls = getattr(hdl, "_gemm_ar_calls", 0)      # per staging buffer: selects the staging half / flag bank
+    hdl._gemm_ar_calls = calls + 1
+    algo = {"one_shot": 0, "two_shot": 1}.get(str(kwargs.get("algo", config.force_algo() or "")), -1)
+    mc = hdl.multicast_ptr or None
+    _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, mc, hdl.rank, hdl.world_size,
+                                 a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
+                                 int(kwargs.get("swap_ab", -1)), algo, calls & 1, config.TILE_FLAG_BASE,
+                                 hdl.signal_pad_words, hdl.buffer_size // 1024 * 1024, _lib.current_stream_ptr()))
     return out
 
 

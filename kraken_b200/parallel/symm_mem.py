@@ -362,16 +362,18 @@ def is_symm_tensor(t: torch.Tensor) -> bool:
 _workspaces: dict[tuple, SymmHandle] = {}
 
 
-def get_symm_mem_workspace(group=None, min_size: int = 0, device=None) -> SymmHandle:
+def get_symm_mem_workspace(group=None, min_size: int = 0, device=None, kind: str = "shared") -> SymmHandle:
     """Per-group symmetric scratch of at least `min_size` bytes. Growth is collective: all ranks
-    must ask for the same size at the same time (they do — ops size it from the op's shape)."""
+    must ask for the same size at the same time (they do — ops size it from the op's shape).
+    `kind` selects a pool: ops that keep state in their scratch between calls (the GEMM all-reduce
+    alternates staging halves) use a pool of their own."""
     info = resolve_group(group)
     if info.emu is not None:
-        return info.emu.workspace(info.rank, min_size)
+        return info.emu.workspace(info.rank, min_size, kind)
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     device = torch.device(device)
-    key = (info.name, device.index)
+    key = (info.name, device.index, kind)
     hdl = _workspaces.get(key)
     if hdl is not None and hdl.buffer_size >= min_size:
         return hdl
@@ -468,12 +470,14 @@ class EmuWorld:
                 return self._handles[idx][rank]
         raise ValueError("tensor is not rank %d's view of an emulated symmetric tensor" % rank)
 
-    def workspace(self, rank: int, min_size: int) -> SymmHandle:
-        if self._ws_handles is None or self._ws_handles[0].buffer_size < min_size:
+    def workspace(self, rank: int, min_size: int, kind: str = "shared") -> SymmHandle:
+        pools = self.__dict__.setdefault("_ws_pools", {})
+        handles = pools.get(kind)
+        if handles is None or handles[0].buffer_size < min_size:
             size = max(int(min_size), 1 << 20)
             idx = self._make_block(size)
-            self._ws_handles = self._handles[idx]
-        return self._ws_handles[rank]
+            handles = pools[kind] = self._handles[idx]
+        return handles[rank]
 
     @contextlib.contextmanager
     def rank(self, r: int):

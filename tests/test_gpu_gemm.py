@@ -172,20 +172,36 @@ def test_gemm_reduce_scatter_unaligned_slab_path(ws):
 
 @pytest.mark.parametrize("ws", [2, 4, 8])
 @pytest.mark.parametrize("M", [1, 16, 64, 256])
-def test_gemm_one_shot_all_reduce(ws, M):
+@pytest.mark.parametrize("algo", ["one_shot", "two_shot"])
+def test_gemm_one_shot_all_reduce(ws, M, algo):
     world = EmuWorld(ws)
     N, Kl = 1024, 256
     g = torch.Generator().manual_seed(9)
     a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
     bt_s = [(0.02 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
     full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
-    for _ in range(2):
-        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t()))
+    for _ in range(3):       # three rounds: both staging halves / flag banks, then reuse of the first
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo=algo))
         for r in range(ws):
             assert outs[r].dtype == torch.float32
             torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
         for r in range(1, ws):
             assert torch.equal(outs[0], outs[r])
+
+
+def test_gemm_all_reduce_alternating_shapes_and_algorithms():
+    # consecutive calls of different shapes and exchange algorithms share one staging buffer
+    ws = 4
+    world = EmuWorld(ws)
+    g = torch.Generator().manual_seed(10)
+    for M, N, algo in [(256, 1024, "two_shot"), (16, 512, "one_shot"), (64, 1024, "two_shot"), (1, 1024, "one_shot"),
+                       (200, 520, "two_shot"), (200, 520, "one_shot")]:
+        a_s = [torch.randn(M, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+        bt_s = [(0.02 * torch.randn(N, 128, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
+        full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo=algo))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
 
 
 def test_gemm_all_reduce_rank_valued_exact():

@@ -147,8 +147,8 @@ def _all_ops(rank, ws):
         ad = torch.randn(Md, 1024, device=dev).to(torch.bfloat16)
         btd = (0.02 * torch.randn(2048, 1024, device=dev)).to(torch.bfloat16)
         gold_d = nccl_sum(ad.float() @ btd.float().t())
-        for _ in range(2):
-            o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t())
+        for algo in ("one_shot", "two_shot", "one_shot", "two_shot", None):
+            o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t(), **({"algo": algo} if algo else {}))
             assert o.dtype == torch.float32
             torch.testing.assert_close(o, gold_d, atol=5e-3, rtol=5e-3)
     ones = torch.ones(32, 32, device=dev, dtype=torch.bfloat16)
