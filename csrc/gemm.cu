@@ -30,7 +30,7 @@ struct PlainHooks {
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols};
+    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
 };
@@ -58,7 +58,7 @@ struct AgHooks {
     return true;
   }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols};
+    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
 };
@@ -87,9 +87,9 @@ struct RsHooks {
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
     const int owner = owner_of(p, tr);
     const int row0 = tr * kBM - owner * p.slab_rows;
-    if (owner == p.rank) return TileDest{(char*)p.out, p.ldo, row0, tc * bn, p.slab_rows, p.rows_c};
+    if (owner == p.rank) return TileDest{(char*)p.out, p.ldo, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[p.ws] : nullptr};
     char* base = (char*)p.bufs[owner] + (size_t)p.rank * p.slab_rows * p.rows_c * 2;
-    return TileDest{base, (long long)p.rows_c, row0, tc * bn, p.slab_rows, p.rows_c};
+    return TileDest{base, (long long)p.rows_c, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[owner] : nullptr};
   }
   // Own tiles: add the peers' staged partial sums (bf16) to the fp32 fragment, in rank order.
   __device__ __forceinline__ void add_to_chunk(const GemmParams& p, int tr, int tc, int row_in_tile, int col_in_tile,
@@ -169,7 +169,7 @@ struct ArHooks {
       const int owner = tile_of(p, tr, tc) % p.ws;
       base = (char*)p.bufs[owner] + p.part_off + (size_t)p.rank * p.out_rows * p.out_cols * 4;
     }
-    return TileDest{base, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols};
+    return TileDest{base, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
   }
   // region of tile (tr, tc) in the orientation of `out`
   __device__ __forceinline__ void region(const GemmParams& p, int tr, int tc, int& r_lo, int& r_n, int& c_lo, int& c_n) {
@@ -336,7 +336,7 @@ struct CeHooks {
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols};
+    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
     epi_bar_sync();
@@ -559,6 +559,22 @@ static int default_group_r() {
   return v;
 }
 
+static bool tma_store_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("KRAKEN_TMA_STORE");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// Tensor map for storing bf16 tiles into a row-major matrix [rows, cols] (row stride ld elements).
+// Returns false (and leaves `m` alone) when the matrix cannot be described to TMA.
+static bool store_tmap(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* m) {
+  if (!tma_store_enabled() || !ptr || ((uintptr_t)ptr & 15) || (ld * 2) % 16 || cols < 1 || rows < 1) return false;
+  return get_tmap(ptr, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, 32, m) == KR_SUCCESS;
+}
+
 static int pick_bn(int rows_c) {
   if (rows_c > 128) return 256;
   if (rows_c > 64) return 128;
@@ -703,6 +719,7 @@ KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long 
   p.out_fp32 = out_fp32;
   p.ws = 1;
   p.sync = sync_ctx(d);
+  if (!swap && !out_fp32 && bn >= 64) p.use_tma_store = store_tmap(out, M, N, ldo, &p.tmap_out[0]) ? 1 : 0;
   unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
   unsigned cap = grid_cap(d);
   if (max_ctas > 0 && (unsigned)max_ctas < cap) cap = (unsigned)max_ctas;
@@ -739,6 +756,7 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   p.ldo = ldc;
   p.out_rows = M;
   p.out_cols = N;
+  if (bn >= 64) p.use_tma_store = store_tmap(c, M, N, ldc, &p.tmap_out[0]) ? 1 : 0;
   p.rank = rank;
   p.ws = ws;
   p.bufs = bufs;
@@ -770,9 +788,10 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
 }
 
 // Fused GEMM -> reduce-scatter. a[M, K_local], bt[N, K_local]; bufs[r] = rank r's staging
-// workspace of at least M*N*2 bytes; out[M/ws, N] bf16. Tile flags live in the signal pads at
+// workspace of at least M*N*2 bytes (bufs: device table; bufs_host: the same addresses in host
+// memory, used to describe the staging slots to TMA, or nullptr); out[M/ws, N] bf16. Tile flags live in the signal pads at
 // word offset flag_base (zero on entry, zero again on exit).
-KR_API int kr_gemm_rs_bf16(void* const* bufs, uint32_t* const* pads, int rank, int ws, const void* a, long long lda,
+KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads, int rank, int ws, const void* a, long long lda,
                            const void* bt, long long ldb, void* out, long long ldo, int M, int N, int K,
                            uint32_t pad_base, uint32_t flag_base, unsigned long long pad_words, cudaStream_t stream) {
   DeviceState* d = device_state();
@@ -801,6 +820,13 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, uint32_t* const* pads, int rank, i
   const int tiles_per_slab = p.slab_rows / kBM;
   KR_REQUIRE((unsigned long long)flag_base + (unsigned long long)tiles_per_slab * p.tiles_c <= pad_words,
              "signal pad too small for the tile flags");
+  // TMA-store destinations: rank o's staging slot [rank] for every o, and the local output.
+  if (bufs_host != nullptr && ws <= 8 && bn >= 64) {
+    bool ok = store_tmap(out, p.slab_rows, N, ldo, &p.tmap_out[ws]);
+    for (int o = 0; o < ws && ok; ++o)
+      ok = store_tmap((const char*)bufs_host[o] + (size_t)rank * p.slab_rows * N * 2, p.slab_rows, N, N, &p.tmap_out[o]);
+    p.use_tma_store = ok ? 1 : 0;
+  }
   p.pivot_r = (((rank + 1) % ws) * tiles_per_slab) % p.tiles_r;   // next rank's slab first, own slab last
   p.group_r = tiles_per_slab >= default_group_r() ? default_group_r() : tiles_per_slab;
   while (tiles_per_slab % p.group_r) --p.group_r;                 // groups never straddle two slabs
@@ -902,6 +928,7 @@ KR_API int kr_gemm_ce_producer_bf16(const void* a, long long lda, const void* bt
   p.ldo = ldo;
   p.out_rows = M;
   p.out_cols = N;
+  if (bn >= 64) p.use_tma_store = store_tmap(gemm_out, M, N, ldo, &p.tmap_out[0]) ? 1 : 0;
   p.rank = rank;
   p.ws = ws;
   p.progress = signals;

@@ -57,6 +57,10 @@ struct alignas(64) GemmParams {
   int out_fp32;              // 1: fp32 output, 0: bf16
   int num_mma_ctas;          // CTAs [0, num_mma_ctas) run the GEMM; the rest are comm CTAs (AG)
   // output (PLAIN / AG / final result of RS and AR)
+  // TMA-store destinations (bf16 row-major): [0] = `out`; GEMM->RS: [o] = rank o's staging slot for
+  // this rank's tiles, [ws] = `out`. Valid when use_tma_store != 0.
+  CUtensorMap tmap_out[9];
+  int use_tma_store;
   void* out;
   long long ldo;             // elements between consecutive output rows
   int out_rows, out_cols;    // bounds of `out` in the orientation it is stored
@@ -115,6 +119,8 @@ struct TileDest {
   long long ld;      // elements per destination row
   int row0, col0;    // where the tile's (0,0) lands in the destination
   int rows, cols;    // destination bounds
+  const CUtensorMap* tmap;   // bf16 destination as a tensor map (box 64 columns x 32 rows, 128-byte
+                             // swizzle) for TMA stores, or nullptr: plain vector stores
 };
 
 // Epilogue of one tile, run by the four epilogue warps: TMEM -> registers -> (hook: add peers'
@@ -155,6 +161,58 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
         }
       }
     }
+  } else if (BN >= 64 && !p.out_fp32 && dst.tmap != nullptr) {
+    // bf16 row-major tile through TMA stores. The warp's 32 rows are staged as panels of 64 columns
+    // (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by row: the layout a 128-byte-swizzle
+    // tensor map expects, and conflict-free for the row-per-lane writes); one elected lane stores
+    // each panel with a single bulk tensor copy, to local or PEER memory. Two panel slots alternate.
+    // The TMA engine keeps far more bytes in flight towards a peer than the SM's store path does.
+    constexpr int PANELS = BN / 64;
+#pragma unroll 1
+    for (int pn = 0; pn < PANELS; ++pn) {
+      unsigned char* slot = stg + (pn & 1) * 4096;
+      if (pn >= 2) {
+        if (lane == 0) bulk_wait_group_read<1>();      // the store that last read this slot is done with it
+        __syncwarp();
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        const int col = pn * 64 + c * 32;
+        tmem_ld32(t_addr + col, r);
+        tmem_ld_wait();
+        if (pn == PANELS - 1 && c == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) { if (PAIR) mbar_arrive_cluster(tempty_addr); else mbar_arrive(tempty_addr); }
+        }
+        hooks.add_to_chunk(p, tr, tc, q * 32 + lane, col, r, 32);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int chunk = c * 4 + u;
+          const int phys = chunk ^ (lane & 7);
+          U4 v;
+          v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+          v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+          v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+          v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+          *(U4*)(slot + lane * 128 + phys * 16) = v;
+        }
+      }
+      fence_proxy_async_smem();       // staged bytes visible to the TMA engine
+      __syncwarp();
+      const int gx = dst.col0 + pn * 64, gy = dst.row0 + q * 32;
+      if (lane == 0 && gx < dst.cols && gy < dst.rows) {
+        tma_store_2d(dst.tmap, smem_u32(slot), gx, gy);
+        bulk_commit_group();
+      }
+    }
+    // the tile's stores must be complete before the hook may tell anyone about them
+    if (lane == 0) {
+      bulk_wait_group<0>();
+      fence_proxy_async();
+    }
+    __syncwarp();
   } else {
     // Row-major store through per-warp staging: 32 rows x 256 bytes, 16-byte units XOR-swizzled
     // by row so that both the row-per-lane writes and the row-contiguous reads are conflict-free.

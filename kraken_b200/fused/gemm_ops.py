@@ -200,7 +200,8 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, s))
     elif (M // ws) % 128 == 0 and N % 8 == 0:
         hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
-        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, hdl.rank, ws, a2.data_ptr(), lda,
+        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev, hdl.rank, ws,
+                                     a2.data_ptr(), lda,
                                      bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, config.TILE_FLAG_BASE,
                                      hdl.signal_pad_words, s))
     else:
