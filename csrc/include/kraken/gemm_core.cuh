@@ -130,7 +130,7 @@ struct TileDest {
 template <int BN, bool PAIR, class Hooks>
 __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& hooks, int tr, int tc, int acc,
                                                    uint32_t tmem_base, int q, int lane, unsigned char* stg,
-                                                   uint32_t tempty_addr) {
+                                                   uint32_t tempty_addr, bool defer) {
   if (!hooks.begin_tile(p, tr, tc, q, lane)) return false;
   TileDest dst = hooks.tile_dest(p, tr, tc);
   const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
@@ -171,10 +171,13 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
 #pragma unroll 1
     for (int pn = 0; pn < PANELS; ++pn) {
       unsigned char* slot = stg + (pn & 1) * 4096;
-      if (pn >= 2) {
-        if (lane == 0) bulk_wait_group_read<1>();      // the store that last read this slot is done with it
-        __syncwarp();
+      // The store that last read this slot (two panels ago, possibly in the previous tile) must be
+      // done with it; only the most recent group (the other slot) may still be reading.
+      if (lane == 0) {
+        if (PANELS == 1) bulk_wait_group_read<0>();
+        else bulk_wait_group_read<1>();
       }
+      __syncwarp();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
@@ -202,14 +205,18 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
       fence_proxy_async_smem();       // staged bytes visible to the TMA engine
       __syncwarp();
       const int gx = dst.col0 + pn * 64, gy = dst.row0 + q * 32;
-      if (lane == 0 && gx < dst.cols && gy < dst.rows) {
-        tma_store_2d(dst.tmap, smem_u32(slot), gx, gy);
-        bulk_commit_group();
+      if (lane == 0) {
+        if (gx < dst.cols && gy < dst.rows) tma_store_2d(dst.tmap, smem_u32(slot), gx, gy);
+        bulk_commit_group();           // one group per panel, empty or not, so groups can be counted
       }
     }
-    // the tile's stores must be complete before the hook may tell anyone about them
+    // A tile's stores must be complete before the hook may tell anyone about them. Waiting for this
+    // tile's own stores would put a peer round trip on every tile's epilogue; in deferred mode the
+    // wait covers the PREVIOUS tile's groups (this tile's PANELS groups stay in flight) and the
+    // caller runs the previous tile's hook.
     if (lane == 0) {
-      bulk_wait_group<0>();
+      if (defer) bulk_wait_group<PANELS>();
+      else bulk_wait_group<0>();
       fence_proxy_async();
     }
     __syncwarp();
@@ -289,7 +296,7 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
       __syncwarp();
     }
   }
-  return hooks.after_store(p, tr, tc, q, lane);
+  return true;
 }
 
 template <int BN, class Hooks>
@@ -393,6 +400,9 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
     // ================= epilogue warps =================
     const int q = warp & 3;                                  // TMEM lane quarter this warp may read
     unsigned char* stg = epi_ptr + (warp - 2) * kEpiWarpBytes;
+    // tiles leave through TMA stores: run each tile's completion hook one tile late (see the epilogue)
+    const bool defer = BN >= 64 && !p.out_fp32 && !p.transposed && p.use_tma_store != 0;
+    int prev_tr = -1, prev_tc = -1;
     int it = 0;
     bool ok = true;
     for (int t = bid; t < total_tiles && ok; t += nb, ++it) {
@@ -404,7 +414,23 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      ok = gemm_epilogue_tile<BN, false>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, tempty_bar(acc));
+      ok = gemm_epilogue_tile<BN, false>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, tempty_bar(acc), defer);
+      if (!ok) break;
+      if (defer) {
+        if (prev_tr >= 0) ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
+        prev_tr = tr;
+        prev_tc = tc;
+      } else {
+        ok = hooks.after_store(p, tr, tc, q, lane);
+      }
+    }
+    if (defer && prev_tr >= 0) {
+      if (lane == 0) {
+        bulk_wait_group<0>();
+        fence_proxy_async();
+      }
+      __syncwarp();
+      if (ok) hooks.after_store(p, prev_tr, prev_tc, q, lane);
     }
   }
 
@@ -558,6 +584,8 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
     const int q = warp & 3;
     unsigned char* stg = epi_ptr + (warp - 2) * kEpiWarpBytes;
     const uint32_t lead_tempty[2] = {mapa_shared(tempty_bar(0), 0), mapa_shared(tempty_bar(1), 0)};
+    const bool defer = !p.out_fp32 && !p.transposed && p.use_tma_store != 0;
+    int prev_tr = -1, prev_tc = -1;
     int it = 0;
     bool ok = true;
     for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++it) {
@@ -570,7 +598,23 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      ok = gemm_epilogue_tile<Cfg::BN, true>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, lead_tempty[acc]);
+      ok = gemm_epilogue_tile<Cfg::BN, true>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, lead_tempty[acc], defer);
+      if (!ok) break;
+      if (defer) {
+        if (prev_tr >= 0) ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
+        prev_tr = tr;
+        prev_tc = tc;
+      } else {
+        ok = hooks.after_store(p, tr, tc, q, lane);
+      }
+    }
+    if (defer && prev_tr >= 0) {
+      if (lane == 0) {
+        bulk_wait_group<0>();
+        fence_proxy_async();
+      }
+      __syncwarp();
+      if (ok) hooks.after_store(p, prev_tr, prev_tc, q, lane);
     }
   }
 

@@ -76,6 +76,9 @@ _PROTOS = {
                                          _P, _P]),
     "kr_symm_barrier": (c_int, [_P, c_int, c_int, c_int, _P]),
     "kr_sync_test": (c_int, [_P, c_int, c_int, _P, _P, c_int, c_int, c_int, _P]),
+    # host model of the barrier protocol
+    "kr_host_barrier": (c_uint32, [_P, c_ulonglong, c_int, c_int, c_int, c_double, c_int, c_int]),
+    "kr_host_pad_nonzero": (c_ulonglong, [_P, c_ulonglong, c_int]),
     # norm kernels
     "kr_rms_norm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "kr_all_reduce_bias_rms_norm": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, c_ulonglong, _P, _P, c_int, c_int, c_float,
