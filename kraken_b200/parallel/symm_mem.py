@@ -377,8 +377,14 @@ def get_symm_mem_workspace(group=None, min_size: int = 0, device=None, kind: str
     hdl = _workspaces.get(key)
     if hdl is not None and hdl.buffer_size >= min_size:
         return hdl
-    size = max(int(min_size), 32 << 20)
+    size = max(int(min_size), int(os.environ.get("KRAKEN_WS_MIN_MB", "32")) << 20)
     size = 1 << (size - 1).bit_length()      # geometric growth: few re-rendezvous
+    pre = int(os.environ.get("KRAKEN_WS_PREALLOC_MB", "0"))
+    if pre > 0 and hdl is None:
+        dummy = SymmAllocation(pre << 20, device)
+        with _alloc_lock:
+            _allocations.append(dummy)
+        dummy.handle = _exchange_and_map(dummy, info)
     alloc = SymmAllocation(size, device)
     with _alloc_lock:
         _allocations.append(alloc)
