@@ -202,7 +202,7 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s (bf16 dense, whole job)", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": Ml * H * 2, "d2h_bytes_per_step": 4},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 2 * args.steps,   # per step: the all-gather GEMM kernel and the reduce-scatter GEMM kernel
             "wall_s": wall,
         }
         print(json.dumps(out), flush=True)

@@ -122,7 +122,14 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     off = hdl.offset_of(a_shared)
     if off:
         raise ValueError("a_shared must start at the beginning of its symmetric buffer")
-    if backend == "ce" and hdl.group.emu is None and ws > 1:
+    if ws == 1 and hdl.group.emu is None:
+        # nothing to gather: a device copy fills a_out while the GEMM reads the shard in place
+        a_out.copy_(a_shared)
+        progress.fill_(1)
+        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
+                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
+                                     progress.data_ptr(), counters.data_ptr(), -1, 0, _lib.current_stream_ptr()))
+    elif backend == "ce" and hdl.group.emu is None and ws > 1:
         from ..comm.all_gather import _copy_engine_all_gather_w_progress
 
         stream = _copy_engine_all_gather_w_progress(a_out, a_shared, progress, splits)
