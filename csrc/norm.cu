@@ -239,11 +239,12 @@ KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot_mc, NormParams, kNormMaxThreads)
 
 using namespace kraken;
 
-static unsigned norm_threads(int D) {
-  // one 16-byte vector per thread while the row fits a block: every load of a row is then in
-  // flight at once, which is what matters when the loads cross NVLink
+// Threads per row. vpt = 16-byte vectors each thread keeps: 1 when the loads cross NVLink (every
+// load of a row in flight at once matters more than occupancy), up to kNormVpt for the local
+// kernel (smaller blocks, several rows resident per SM, four independent loads per thread).
+static unsigned norm_threads(int D, int vpt) {
   unsigned nvec = (unsigned)D / 8;
-  unsigned t = nvec;
+  unsigned t = (nvec + vpt - 1) / vpt;
   t = (t + 31) / 32 * 32;
   if (t < 64) t = 64;
   if (t > kNormMaxThreads) t = kNormMaxThreads;
@@ -259,9 +260,12 @@ KR_API int kr_rms_norm(const void* x, const void* w, void* y, int rows, int D, f
   NormParams p;
   memset(&p, 0, sizeof(p));
   p.x = x; p.y = y; p.w = w; p.rows = rows; p.D = D; p.eps = eps;
-  unsigned nb = rows < d->num_sms * 4 ? (unsigned)rows : (unsigned)d->num_sms * 4;
+  const unsigned nt = norm_threads(D, rows >= 2 * d->num_sms ? kNormVpt : 1);
+  const unsigned resident = 2048 / nt > 0 ? 2048 / nt : 1;
+  const unsigned cap = (unsigned)d->num_sms * resident;
+  unsigned nb = (unsigned)rows < cap ? (unsigned)rows : cap;
   if (D / 8 <= kNormVpt * kNormMaxThreads)
-    rms_norm_kernel<<<nb, norm_threads(D), 0, stream>>>(p);
+    rms_norm_kernel<<<nb, nt, 0, stream>>>(p);
   else
     rms_norm_long_kernel<<<nb, kNormMaxThreads, 0, stream>>>(p);
   KR_CUDA(cudaGetLastError());
@@ -294,7 +298,7 @@ KR_API int kr_all_reduce_bias_rms_norm(void* const* bufs, unsigned long long buf
   unsigned cap = (unsigned)d->num_sms;
   if (emu_recorder().active) cap = cap / (unsigned)emu_recorder().ws ? cap / (unsigned)emu_recorder().ws : 1;
   unsigned nb = (unsigned)rows < cap ? (unsigned)rows : cap;
-  unsigned nt = norm_threads(D);
+  unsigned nt = norm_threads(D, 1);
   if (algo == 0) return launch_ranked(ar_norm_one_shot_kernel, ar_norm_one_shot_emu_kernel, p, nb, nt, 0, stream);
   if (algo == 1) return launch_ranked(ar_norm_two_shot_kernel, ar_norm_two_shot_emu_kernel, p, nb, nt, 0, stream);
   return launch_ranked(ar_norm_two_shot_mc_kernel, ar_norm_two_shot_mc_emu_kernel, p, nb, nt, 0, stream);
