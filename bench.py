@@ -139,7 +139,7 @@ def run_ours(args):
     if ws > 1:
         # Untimed shape warm-up: one reduce-scatter GEMM at a quarter of the rows first. At 8 GPUs the
         # M = 8192 op measured 330 us when a smaller one had run before it in the process and 530 us
-        # when it was the first to use the staging workspace (cause not yet found; see DESIGN.md).
+        # when it was the first to use the staging workspace (cause not yet found).
         fused.gemm_reduce_scatter(h_small, w_down_t.t())
     for _ in range(max(3, args.warmup)):
         step()

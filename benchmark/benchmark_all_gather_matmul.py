@@ -19,7 +19,7 @@ def main():
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--N", type=int, default=28672, help="global N; each rank holds N / world_size columns")
     ap.add_argument("--iters", type=int, default=15)
-    ap.add_argument("--save-path", default="gpurun_out/bench_all_gather_matmul")
+    ap.add_argument("--save-path", default="results/bench_all_gather_matmul")
     args = ap.parse_args()
     rank, ws, dev = setup()
     from kraken_b200 import fused

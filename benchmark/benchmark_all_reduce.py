@@ -21,7 +21,7 @@ def main():
     ap.add_argument("--max-bytes", type=int, default=256 << 20)
     ap.add_argument("--backend", nargs="*", default=None)
     ap.add_argument("--iters", type=int, default=25)
-    ap.add_argument("--save-path", default="gpurun_out/bench_all_reduce")
+    ap.add_argument("--save-path", default="results/bench_all_reduce")
     args = ap.parse_args()
     rank, ws, dev = setup()
     from kraken_b200 import comm

@@ -17,7 +17,7 @@ def main():
     ap.add_argument("--max-b", type=int, default=512)
     ap.add_argument("--d-size", type=int, default=5120)
     ap.add_argument("--iters", type=int, default=50)
-    ap.add_argument("--save-path", default="gpurun_out/bench_all_reduce_bias_rms_norm")
+    ap.add_argument("--save-path", default="results/bench_all_reduce_bias_rms_norm")
     args = ap.parse_args()
     rank, ws, dev = setup()
     from kraken_b200 import fused

@@ -18,7 +18,7 @@ def main():
     ap.add_argument("--K", type=int, default=8192, help="global K; each rank holds K / world_size")
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=50)
-    ap.add_argument("--save-path", default="gpurun_out/bench_decode_block")
+    ap.add_argument("--save-path", default="results/bench_decode_block")
     args = ap.parse_args()
     rank, ws, dev = setup()
     from kraken_b200 import fused
