@@ -119,6 +119,8 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     backend = kwargs.get("backend", config.ag_mode())
     counters = _zero_counters(a_shared.device, ws * splits, hdl.group.emu)
     L = _lib.lib()
+    if config.dump_kernel() and rank == 0:
+        print(f"[kraken_b200] all_gather_matmul M={M} N={N} K={K} ws={ws} splits={splits} engine={backend}", flush=True)
     off = hdl.offset_of(a_shared)
     if off:
         raise ValueError("a_shared must start at the beginning of its symmetric buffer")
@@ -201,6 +203,10 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
         raise ValueError("M must be divisible by the world size")
     out_dtype = a.dtype if a.dtype in (torch.bfloat16,) else torch.bfloat16
     out = torch.empty((M // ws, N), dtype=out_dtype, device=a.device)
+    if config.dump_kernel() and info.rank == 0:
+        path = "plain GEMM" if ws == 1 else ("fused epilogue push" if (M // ws) % 128 == 0 and N % 8 == 0
+                                             else "GEMM + reduce-scatter kernel")
+        print(f"[kraken_b200] gemm_reduce_scatter M={M} N={N} K={K} ws={ws}: {path}", flush=True)
     L = _lib.lib()
     s = _lib.current_stream_ptr()
     if ws == 1:
