@@ -128,10 +128,22 @@ _alloc_lock = threading.Lock()
 _rdv_seq = itertools.count()
 
 
+_alloc_by_ptr: dict[tuple, SymmAllocation | None] = {}
+
+
 def _find_allocation(t: torch.Tensor) -> SymmAllocation | None:
+    """Allocation that holds tensor `t` (ops call this on every invocation: hits are cached by
+    data pointer; misses are not cached because ordinary memory is recycled by torch's allocator)."""
     ptr = t.data_ptr()
+    key = (t.device.index, ptr)
+    hit = _alloc_by_ptr.get(key)
+    if hit is not None:
+        return hit
     for a in _allocations:
         if a.device == t.device and a.contains(ptr):
+            if len(_alloc_by_ptr) > 4096:
+                _alloc_by_ptr.clear()
+            _alloc_by_ptr[key] = a
             return a
     return None
 
