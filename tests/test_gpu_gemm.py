@@ -214,3 +214,20 @@ def test_gemm_all_reduce_rank_valued_exact():
     expect = torch.full((n, n), float(n * sum(range(1, ws + 1))), device="cuda")
     for r in range(ws):
         torch.testing.assert_close(outs[r], expect, atol=1e-5, rtol=1e-5)
+
+
+def test_tensor_map_cache_is_hit_on_repeated_calls():
+    import ctypes
+
+    from kraken_b200.ops import lib as klib
+
+    a, bt = _ab(512, 512, 256, seed=13)
+    fused.matmul(a, bt.t())
+    h0, m0 = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    klib.check(klib.lib().kr_tmap_cache_stats(ctypes.byref(h0), ctypes.byref(m0)))
+    for _ in range(5):
+        fused.matmul(a, bt.t())
+    h1, m1 = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+    klib.check(klib.lib().kr_tmap_cache_stats(ctypes.byref(h1), ctypes.byref(m1)))
+    assert h1.value - h0.value >= 10           # both operand maps, five calls
+    assert m1.value - m0.value <= 5            # at most the output map of a fresh output tensor
