@@ -23,7 +23,6 @@ def main():
     rank, ws, dev = setup()
     from kraken_b200 import fused
     from kraken_b200.parallel import symm_mem
-    import torch.distributed._symmetric_memory as tsm
 
     ref, why = load_reference()
     pk = peaks()

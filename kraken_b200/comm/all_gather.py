@@ -15,7 +15,6 @@ import ctypes
 import torch
 
 from .. import _reference as ref
-from .. import config
 from ..ops import lib as _lib
 from ..parallel import symm_mem
 

@@ -25,7 +25,7 @@ import ctypes
 import itertools
 import os
 import threading
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
@@ -433,8 +433,7 @@ class EmuWorld:
         self._handles: dict[int, list[SymmHandle]] = {}
         self._by_kind: dict[tuple, list[int]] = {}
         self._requests: dict[tuple, int] = {}
-        self._ws_blocks: list[SymmAllocation] | None = None
-        self._ws_handles: list[SymmHandle] | None = None
+        self._ws_pools: dict[str, list[SymmHandle]] = {}
         self._keep = []
 
     def _make_block(self, nbytes: int) -> int:
@@ -489,7 +488,7 @@ class EmuWorld:
         raise ValueError("tensor is not rank %d's view of an emulated symmetric tensor" % rank)
 
     def workspace(self, rank: int, min_size: int, kind: str = "shared") -> SymmHandle:
-        pools = self.__dict__.setdefault("_ws_pools", {})
+        pools = self._ws_pools
         handles = pools.get(kind)
         if handles is None or handles[0].buffer_size < min_size:
             size = max(int(min_size), 1 << 20)
