@@ -13,3 +13,11 @@ __all__ = [
     "reduce_scatter",
     "two_shot_all_reduce",
 ]
+
+# optional NVTX ranges (KRAKEN_NVTX=1): wrap the public callables of this module
+from ..utils.nvtx import nvtx_range as _nvtx_range  # noqa: E402
+
+for _name in list(__all__):
+    _obj = globals()[_name]
+    if callable(_obj):
+        globals()[_name] = _nvtx_range(_obj)

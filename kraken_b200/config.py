@@ -7,9 +7,13 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_NVLS``             ``0`` disables NVLS multicast binding and the multimem kernels (default 1)
 ``KRAKEN_SIGNAL_PAD_BYTES`` signal-pad size of blocks from the native allocator (default 1 MiB)
 ``KRAKEN_FORCE_ALGO``       ``one_shot`` / ``two_shot`` / ``multimem``: overrides all-reduce selection
-``KRAKEN_NUM_COMM_SMS``     comm CTAs of the fused all-gather GEMM (default 8)
+``KRAKEN_NUM_COMM_SMS``     comm CTAs of the in-kernel all-gather engine (default: from the problem shape)
+``KRAKEN_GEMM_PAIR``        ``0`` forces the single-CTA GEMM kernel (default: CTA pairs when eligible)
+``KRAKEN_GEMM_GROUP``       row tiles per column sweep of the GEMM tile order (default 16)
+``KRAKEN_TMA_STORE``        ``0`` makes the GEMM epilogue use vector stores instead of TMA stores
 ``KRAKEN_AG_MODE``          ``ce`` (copy engines + stream flags feed the GEMM kernel, default) or ``sm`` (comm CTAs
                             inside the GEMM kernel pull the shards)
+``KRAKEN_NVTX``             ``1`` wraps every public op in an NVTX range named after it (for timeline tools)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
 ``BENCHMARK_ITERS``         overrides the iteration count of the timing harness
@@ -59,6 +63,10 @@ def ag_mode() -> str:
 
 def dump_kernel() -> bool:
     return os.environ.get("KRAKEN_DUMP_KERNEL", "0") == "1"
+
+
+def nvtx_enabled() -> bool:
+    return os.environ.get("KRAKEN_NVTX", "0") == "1"
 
 
 def symm_backend() -> str:
