@@ -946,3 +946,17 @@ KR_API int kr_gemm_ce_producer_bf16(const void* a, long long lda, const void* bt
   p.num_mma_ctas = (int)nb;
   return launch_gemm(bn, p, nb, stream);
 }
+
+// Host evaluation of the persistent tile order (the same function the kernels run): writes
+// (row tile, column tile) of linear tile t to out[2t], out[2t+1]. For tests of the index math.
+KR_API int kr_tile_order(int tiles_r, int tiles_c, int group_r, int pivot_r, int* out) {
+  KR_REQUIRE(tiles_r >= 1 && tiles_c >= 1 && group_r >= 1 && pivot_r >= 0 && pivot_r < tiles_r, "bad tiling");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_r = tiles_r;
+  p.tiles_c = tiles_c;
+  p.group_r = group_r;
+  p.pivot_r = pivot_r;
+  for (int t = 0; t < tiles_r * tiles_c; ++t) tile_coords(p, t, out[2 * t], out[2 * t + 1]);
+  return KR_SUCCESS;
+}

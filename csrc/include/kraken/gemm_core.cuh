@@ -94,11 +94,11 @@ struct alignas(64) GemmParams {
 // Linear persistent tile index -> (row tile, column tile): row tiles advance in groups of
 // `group_r` so that concurrently running CTAs share operand tiles in L2, then the row index is
 // rotated by `pivot_r` (rank pivot of the fused kernels).
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tr, int& tc) {
+__host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tr, int& tc) {
   const int per_group = p.group_r * p.tiles_c;
   const int g = t / per_group;
   const int first = g * p.group_r;
-  const int gsz = min(p.tiles_r - first, p.group_r);
+  const int gsz = (p.tiles_r - first) < p.group_r ? (p.tiles_r - first) : p.group_r;
   const int in = t - g * per_group;
   tr = first + in % gsz;
   tc = in / gsz;

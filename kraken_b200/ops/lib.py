@@ -95,6 +95,7 @@ _PROTOS = {
                                 c_int, c_int, c_int, c_int, c_uint32, c_ulonglong, c_ulonglong, _P]),
     "kr_gemm_ce_producer_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int,
                                          c_int, _P, _P, _P]),
+    "kr_tile_order": (c_int, [c_int, c_int, c_int, c_int, _P]),
     "kr_reduce_slabs": (c_int, [_P, _P, c_int, c_int, c_ulonglong, _P]),
 }
 
