@@ -185,9 +185,12 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
 
 
 def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
-    """[M/ws, N] = reduce_scatter(a @ b) along M. The GEMM epilogue pushes every finished tile
-    into its owner's staging slab over NVLink; owners sum the ws slabs in rank order. Shapes whose
-    slab is not a multiple of 128 rows run GEMM -> symmetric staging -> reduce-scatter kernel."""
+    """[M/ws, N] = reduce_scatter(a @ b) along M, in one kernel. Tile order: the next rank's slab
+    first, the own slab last. The epilogue TMA-stores every remote tile into its owner's staging
+    slab over NVLink and bumps the owner's per-tile flag; for own tiles it waits for the flag, adds
+    the peers' staged partial sums to the accumulator in rank order (bit-reproducible) and writes
+    the final rows. Shapes whose slab is not a multiple of 128 rows run GEMM -> symmetric staging
+    -> reduce-scatter kernel."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_reduce_scatter(a, b, group)
