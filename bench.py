@@ -130,17 +130,11 @@ def run_ours(args):
         fused.all_gather_matmul(x_symm, w_up_t.t(), a_out=a_out, progress=progress)
 
     h_fixed = (torch.randn(M, Fl, generator=g).to(torch.bfloat16)).to(dev)
-    h_small = h_fixed[: M // 4].contiguous()
 
     def op_rs():
         fused.gemm_reduce_scatter(h_fixed, w_down_t.t())
 
     sampler = ClockSampler(gpu_index=dev.index).start() if rank == 0 else None
-    if ws > 1:
-        # Untimed shape warm-up: one reduce-scatter GEMM at a quarter of the rows first. At 8 GPUs the
-        # M = 8192 op measured 330 us when a smaller one had run before it in the process and 530 us
-        # when it was the first to use the staging workspace (cause not yet found).
-        fused.gemm_reduce_scatter(h_small, w_down_t.t())
     for _ in range(max(3, args.warmup)):
         step()
     sync()

@@ -16,15 +16,14 @@
 #include <map>
 #include <mutex>
 #include <tuple>
-#include "kraken/driver_api.h"
-#include "kraken/gemm_core.cuh"
+#include "kraken/gemm_host.h"
 
 namespace kraken {
 
 // ---------------------------------------------------------------------------------------------
 // hooks
 // ---------------------------------------------------------------------------------------------
-struct PlainHooks {
+struct PlainHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
@@ -35,7 +34,7 @@ struct PlainHooks {
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
 };
 
-struct AgHooks {
+struct AgHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
@@ -63,86 +62,6 @@ struct AgHooks {
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
 };
 
-struct RsHooks {
-  int bn;
-  __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
-  __device__ __forceinline__ int owner_of(const GemmParams& p, int tr) const { return (tr * kBM) / p.slab_rows; }
-  __device__ __forceinline__ int local_tile(const GemmParams& p, int tr, int tc) const {
-    return (tr - owner_of(p, tr) * (p.slab_rows / kBM)) * p.tiles_c + tc;
-  }
-  // Own-slab tiles are computed last; by then the peers (which computed this slab earlier in their
-  // own order) have pushed their partial tiles. Wait for all ws-1 of them, then consume the flag.
-  __device__ __forceinline__ bool begin_tile(const GemmParams& p, int tr, int tc, int q, int lane) {
-    if (owner_of(p, tr) != p.rank || p.ws == 1) return true;
-    uint32_t* f = p.pads[p.rank] + p.flag_base + local_tile(p, tr, tc);
-    const uint32_t need = (uint32_t)(p.ws - 1);
-    if (lane == 0)
-      spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 55, 0, blockIdx.x));
-    __syncwarp();
-    epi_bar_sync();                       // every epilogue warp has seen the flag
-    if (q == 0 && lane == 0) red_add_relaxed_sys(f, 0u - need);
-    return status_ok(p.sync);
-  }
-  // Remote tiles go to slot `rank` of the owner's staging [ws][slab_rows][N]; own tiles go to `out`.
-  __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    const int owner = owner_of(p, tr);
-    const int row0 = tr * kBM - owner * p.slab_rows;
-    if (owner == p.rank) return TileDest{(char*)p.out, p.ldo, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[p.ws] : nullptr};
-    char* base = (char*)p.bufs[owner] + (size_t)p.rank * p.slab_rows * p.rows_c * 2;
-    return TileDest{base, (long long)p.rows_c, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[owner] : nullptr};
-  }
-  // Own tiles: add the peers' staged partial sums (bf16) to the fp32 fragment, in rank order.
-  __device__ __forceinline__ void add_to_chunk(const GemmParams& p, int tr, int tc, int row_in_tile, int col_in_tile,
-                                               uint32_t (&r)[32], int n) {
-    if (owner_of(p, tr) != p.rank || p.ws == 1) return;
-    const int row = tr * kBM - p.rank * p.slab_rows + row_in_tile;
-    const int col = tc * bn + col_in_tile;
-    if (row >= p.slab_rows) return;
-    const char* stage = (const char*)p.bufs[p.rank];
-    const size_t slab_bytes = (size_t)p.slab_rows * p.rows_c * 2;
-    const size_t off = ((size_t)row * p.rows_c + col) * 2;
-    // Peers in batches of four: the 16 loads of a batch are issued before the first add, so a chunk
-    // costs ceil((ws-1)/4) memory round trips instead of ws-1. The order of the adds stays rank order.
-    for (int s0 = 0; s0 < p.ws; s0 += 4) {
-      U4 x[4][4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int s = s0 + k;
-        if (s < p.ws && s != p.rank) {
-          const char* src = stage + (size_t)s * slab_bytes + off;
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (u * 8 < n && col + u * 8 < p.rows_c) x[k][u] = ld16(src + u * 16);   // N % 8 == 0: units are all-in or all-out
-        }
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int s = s0 + k;
-        if (s < p.ws && s != p.rank) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (u * 8 < n && col + u * 8 < p.rows_c) {
-              const uint32_t w[4] = {x[k][u].x, x[k][u].y, x[k][u].z, x[k][u].w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                r[u * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e]) + bf16lo(w[e]));
-                r[u * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e + 1]) + bf16hi(w[e]));
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-  __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
-    const int owner = owner_of(p, tr);
-    if (owner == p.rank) return true;
-    epi_bar_sync();   // all four epilogue warps have issued their stores of this tile
-    if (q == 0 && lane == 0) red_add_release_sys(p.pads[owner] + p.flag_base + local_tile(p, tr, tc), 1u);
-    return true;
-  }
-};
-
 // GEMM -> all-reduce (decode). Two exchange algorithms behind the same main loop:
 //  * one-shot (small M): the fp32 partial tile goes to the rank's OWN staging, a flag goes to
 //    every peer, and every rank sums the tile from all ranks (in-switch with multimem.ld_reduce
@@ -155,7 +74,7 @@ struct RsHooks {
 // The staging buffer is dedicated to this op. One-shot alternates between two staging halves and
 // two flag banks from call to call, and in two-shot nobody leaves before every tile it takes part
 // in is published, so neither needs an exit barrier.
-struct ArHooks {
+struct ArHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
@@ -330,7 +249,7 @@ struct ArHooks {
 // (reference: gemm_reduce_scatter_ce_persistent.py:46-134): tiles go to the local gemm_out; a
 // per-destination counter tracks finished tiles and the tile that completes a slab raises that
 // slab's signal word to 1 with system-scope release, which a stream wait on the host side consumes.
-struct CeHooks {
+struct CeHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
@@ -432,25 +351,24 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
   extern __shared__ unsigned char smem_raw[];
   const unsigned n_mma = (unsigned)p.num_mma_ctas;
   if (p.mode == GEMM_PLAIN) {
-    PlainHooks h{BN};
+    PlainHooks h;
+    h.bn = BN;
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
       ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
-      AgHooks h{BN};
+      AgHooks h;
+    h.bn = BN;
       gemm_mainloop<BN>(p, bid, n_mma, h, smem_raw);
     }
-  } else if (p.mode == GEMM_RS) {
-    RsHooks h{BN};
-    gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
-    // staging slabs and flags may be reused by the next launch only after every rank is done
-    symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
   } else if (p.mode == GEMM_CE) {
-    CeHooks h{BN};
+    CeHooks h;
+    h.bn = BN;
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   } else {
-    ArHooks h{BN};
+    ArHooks h;
+    h.bn = BN;
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   }
 }
@@ -460,21 +378,20 @@ __device__ __forceinline__ void gemm_pair_body(const GemmParams& p, unsigned bid
   extern __shared__ unsigned char smem_raw[];
   const unsigned n_mma = (unsigned)p.num_mma_ctas;   // even
   if (p.mode == GEMM_PLAIN) {
-    PlainHooks h{256};
+    PlainHooks h;
+    h.bn = 256;
     gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
       ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
-      AgHooks h{256};
+      AgHooks h;
+    h.bn = 256;
       gemm_mainloop_pair(p, bid / 2, n_mma / 2, h, smem_raw);
     }
-  } else if (p.mode == GEMM_RS) {
-    RsHooks h{256};
-    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
-    symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
   } else {
-    CeHooks h{256};
+    CeHooks h;
+    h.bn = 256;
     gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
   }
 }
@@ -513,7 +430,7 @@ static unsigned long long g_tmap_hits = 0, g_tmap_misses = 0;
 
 // Tensor map of a row-major bf16 matrix [rows, cols] (cols contiguous, `ld` elements per row),
 // box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range elements read as zero.
-static int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
                     unsigned box_rows, CUtensorMap* out) {
   TmapKey key{ptr, rows, cols, ld, box_rows};
   {
@@ -549,7 +466,7 @@ static int get_tmap(const void* ptr, unsigned long long rows, unsigned long long
 // Row tiles (of 128 rows) that share one sweep over the column tiles. Larger groups re-read the
 // column operand from DRAM fewer times; the group's rows (group * 128 * K * 2 bytes) should stay
 // well inside the 126 MB L2. KRAKEN_GEMM_GROUP overrides for tuning.
-static int default_group_r() {
+int default_group_r() {
   static int v = 0;
   if (v == 0) {
     const char* e = getenv("KRAKEN_GEMM_GROUP");
@@ -570,7 +487,7 @@ static bool tma_store_enabled() {
 
 // Tensor map for storing bf16 tiles into a row-major matrix [rows, cols] (row stride ld elements).
 // Returns false (and leaves `m` alone) when the matrix cannot be described to TMA.
-static bool store_tmap(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* m) {
+bool store_tmap(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* m) {
   if (!tma_store_enabled() || !ptr || ((uintptr_t)ptr & 15) || (ld * 2) % 16 || cols < 1 || rows < 1) return false;
   return get_tmap(ptr, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, 32, m) == KR_SUCCESS;
 }
@@ -586,7 +503,7 @@ static int pick_bn(int rows_c) {
 constexpr size_t kAgSmem = (size_t)kAgSlots * kAgPiece + 1024 + 128;
 static_assert(kAgSmem <= (size_t)kSmemLimit, "comm ring exceeds shared memory");
 
-static bool pair_enabled() {
+bool pair_enabled() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("KRAKEN_GEMM_PAIR");
@@ -602,7 +519,7 @@ static bool pair_eligible(int bn, const GemmParams& p) {
   if (!pair_enabled() || emu_recorder().active) return false;
   if (bn != 256 || p.transposed || p.rows_r < 256) return false;
   if (p.mode == GEMM_AR) return false;
-  if ((p.mode == GEMM_RS || p.mode == GEMM_CE) && (p.slab_rows % 256) != 0) return false;
+  if (p.mode == GEMM_CE && (p.slab_rows % 256) != 0) return false;
   return true;
 }
 
@@ -613,7 +530,7 @@ static int launch_pair(GemmParams p, unsigned cap, unsigned n_comm, cudaStream_t
   p.tiles_r = (p.rows_r + 255) / 256;
   p.pivot_r = p.tiles_r > 0 ? (p.pivot_r / 2) % p.tiles_r : 0;
   p.group_r = p.group_r >= 2 ? p.group_r / 2 : 1;
-  if (p.mode == GEMM_RS || p.mode == GEMM_CE) {
+  if (p.mode == GEMM_CE) {
     const int per_slab = p.slab_rows / 256;
     if (p.group_r > per_slab) p.group_r = per_slab;
     while (per_slab % p.group_r) --p.group_r;
@@ -649,7 +566,7 @@ static int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t st
   }
 }
 
-static unsigned grid_cap(const DeviceState* d) {
+unsigned grid_cap(const DeviceState* d) {
   unsigned cap = (unsigned)d->num_sms;
   if (emu_recorder().active) {
     cap /= (unsigned)emu_recorder().ws;
@@ -660,7 +577,7 @@ static unsigned grid_cap(const DeviceState* d) {
 
 // Fills the operand/tiling part of the parameter block for C[M,N] = A[M,K] * Bt[N,K]^T.
 // swap: the weights (Bt) become the 128-row operand and the tile is stored transposed.
-static int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, long long ldb, int M, int N,
+int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, long long ldb, int M, int N,
                          int K, bool swap, int bn_override, int* bn_out) {
   KR_REQUIRE(M >= 1 && N >= 1 && K >= 8 && K % 8 == 0, "GEMM needs K % 8 == 0 and positive sizes");
   const void* r = swap ? bt : a;
@@ -787,59 +704,6 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   return launch_gemm(bn, p, n_mma + n_comm, stream);
 }
 
-// Fused GEMM -> reduce-scatter. a[M, K_local], bt[N, K_local]; bufs[r] = rank r's staging
-// workspace of at least M*N*2 bytes (bufs: device table; bufs_host: the same addresses in host
-// memory, used to describe the staging slots to TMA, or nullptr); out[M/ws, N] bf16. Tile flags live in the signal pads at
-// word offset flag_base (zero on entry, zero again on exit).
-KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads, int rank, int ws, const void* a, long long lda,
-                           const void* bt, long long ldb, void* out, long long ldo, int M, int N, int K,
-                           uint32_t pad_base, uint32_t flag_base, unsigned long long pad_words, cudaStream_t stream) {
-  DeviceState* d = device_state();
-  if (!d) return KR_FAIL_CUDA;
-  KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
-  KR_REQUIRE(M % ws == 0 && (M / ws) % kBM == 0, "fused GEMM reduce-scatter needs (M / world_size) % 128 == 0");
-  KR_REQUIRE(N % 8 == 0, "fused GEMM reduce-scatter needs N % 8 == 0");
-  KR_REQUIRE(pad_base % ws == 0, "pad_base must be a multiple of the world size");
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  int bn = 0;
-  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, false, N >= 256 ? 256 : 0, &bn);
-  if (rc) return rc;
-  p.mode = GEMM_RS;
-  p.out = out;
-  p.ldo = ldo;
-  p.out_rows = M / ws;
-  p.out_cols = N;
-  p.rank = rank;
-  p.ws = ws;
-  p.bufs = bufs;
-  p.pads = pads;
-  p.pad_base = pad_base;
-  p.flag_base = flag_base;
-  p.slab_rows = M / ws;
-  const int tiles_per_slab = p.slab_rows / kBM;
-  KR_REQUIRE((unsigned long long)flag_base + (unsigned long long)tiles_per_slab * p.tiles_c <= pad_words,
-             "signal pad too small for the tile flags");
-  // TMA-store destinations: rank o's staging slot [rank] for every o, and the local output.
-  if (bufs_host != nullptr && ws <= 8 && bn >= 64) {
-    bool ok = store_tmap(out, p.slab_rows, N, ldo, &p.tmap_out[ws]);
-    for (int o = 0; o < ws && ok; ++o)
-      ok = store_tmap((const char*)bufs_host[o] + (size_t)rank * p.slab_rows * N * 2, p.slab_rows, N, N, &p.tmap_out[o]);
-    p.use_tma_store = ok ? 1 : 0;
-  }
-  p.pivot_r = (((rank + 1) % ws) * tiles_per_slab) % p.tiles_r;   // next rank's slab first, own slab last
-  p.group_r = tiles_per_slab >= default_group_r() ? default_group_r() : tiles_per_slab;
-  while (tiles_per_slab % p.group_r) --p.group_r;                 // groups never straddle two slabs
-  p.sync = sync_ctx(d);
-  unsigned nb = (unsigned)(p.tiles_r * p.tiles_c);
-  unsigned cap = grid_cap(d);
-  if (nb > cap) nb = cap;
-  KR_REQUIRE((unsigned long long)pad_base + (unsigned long long)cap * ws <= flag_base, "barrier slots overlap tile flags");
-  if (pair_eligible(bn, p) && cap >= 2) return launch_pair(p, cap, 0, stream);
-  p.num_mma_ctas = (int)nb;
-  return launch_gemm(bn, p, nb, stream);
-}
-
 // Fused GEMM -> all-reduce (decode). bufs[r] = rank r's staging buffer of staging_bytes, DEDICATED
 // to this op (nothing else may write it between calls); needs staging_bytes >= 2*(ws+1)*M*N*4.
 // out[M, N] fp32 =
@@ -949,14 +813,16 @@ KR_API int kr_gemm_ce_producer_bf16(const void* a, long long lda, const void* bt
 
 // Host evaluation of the persistent tile order (the same function the kernels run): writes
 // (row tile, column tile) of linear tile t to out[2t], out[2t+1]. For tests of the index math.
-KR_API int kr_tile_order(int tiles_r, int tiles_c, int group_r, int pivot_r, int* out) {
+KR_API int kr_tile_order(int tiles_r, int tiles_c, int group_r, int pivot_r, int interleave_r, int* out) {
   KR_REQUIRE(tiles_r >= 1 && tiles_c >= 1 && group_r >= 1 && pivot_r >= 0 && pivot_r < tiles_r, "bad tiling");
+  KR_REQUIRE(interleave_r <= 1 || tiles_r % interleave_r == 0, "interleave must divide the row tiles");
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.tiles_r = tiles_r;
   p.tiles_c = tiles_c;
   p.group_r = group_r;
   p.pivot_r = pivot_r;
+  p.interleave_r = interleave_r;
   for (int t = 0; t < tiles_r * tiles_c; ++t) tile_coords(p, t, out[2 * t], out[2 * t + 1]);
   return KR_SUCCESS;
 }

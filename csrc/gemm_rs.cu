@@ -1,0 +1,445 @@
+// Fused GEMM -> reduce-scatter on the tcgen05 main loop (reference:
+// kraken/fused/gemm_reduce_scatter_fused.py:152-235, gemm_reduce_scatter_ce_persistent.py:326-375).
+// C[M, N] = A[M, K_local] * Bt[N, K_local]^T is a partial sum on every rank; rank r ends up with
+// rows [r*M/ws, (r+1)*M/ws) of the sum over ranks. Two exchange algorithms share the main loop:
+//
+//  * pull (default): every rank TMA-stores ALL its partial tiles into its OWN symmetric staging
+//    matrix [M][N] (local traffic only, the epilogue never touches NVLink) and bumps a per-tile
+//    arrival counter in the tile owner's signal pad. Four extra "reducer" warps per CTA serve the
+//    tiles this rank owns: wait until all ws ranks have stored a tile, then sum it across ranks —
+//    in the NVSwitch with multimem.ld_reduce when the staging buffer has a multicast mapping,
+//    else with ws peer loads in rank order — and write the final rows. All ranks walk the tiles in
+//    the same order with the owners interleaved, so every owner's tiles complete at an even rate
+//    and the reduction of one tile overlaps the MMAs of the following ones. Staging halves and
+//    counter banks alternate call by call, so there is no grid-wide or cross-rank barrier at all.
+//  * push: the epilogue TMA-stores each remote tile into the owner's staging slab [src][M/ws][N]
+//    over NVLink and bumps the owner's counter; own-slab tiles are computed last, their epilogue
+//    waits for the ws-1 peers, adds the staged partial sums to the accumulator fragment in rank
+//    order and writes the final rows. A per-block exit barrier protects the staging slabs.
+#include "kraken/gemm_host.h"
+
+namespace kraken {
+
+constexpr int kRsReducerThreads = 128;
+constexpr int kRsPullThreads = kGemmThreads + kRsReducerThreads;
+
+__device__ __forceinline__ void reducer_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+// push: remote tiles go to the owner's staging slab, own tiles reduce in the epilogue
+// ---------------------------------------------------------------------------------------------
+struct RsPushHooks : HookDefaults {
+  int bn;
+  __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
+  __device__ __forceinline__ int owner_of(const GemmParams& p, int tr) const { return (tr * kBM) / p.slab_rows; }
+  __device__ __forceinline__ int local_tile(const GemmParams& p, int tr, int tc) const {
+    return (tr - owner_of(p, tr) * (p.slab_rows / kBM)) * p.tiles_c + tc;
+  }
+  // begin_tile of an own-slab tile blocks until the peers have pushed their partial tiles
+  __device__ __forceinline__ bool may_wait(const GemmParams& p, int tr) const { return p.ws > 1 && owner_of(p, tr) == p.rank; }
+  __device__ __forceinline__ bool begin_tile(const GemmParams& p, int tr, int tc, int q, int lane) {
+    if (owner_of(p, tr) != p.rank || p.ws == 1) return true;
+    uint32_t* f = p.pads[p.rank] + p.flag_base + local_tile(p, tr, tc);
+    const uint32_t need = (uint32_t)(p.ws - 1);
+    if (lane == 0)
+      spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 55, 0, blockIdx.x));
+    __syncwarp();
+    epi_bar_sync();                       // every epilogue warp has seen the flag
+    if (q == 0 && lane == 0) red_add_relaxed_sys(f, 0u - need);
+    return status_ok(p.sync);
+  }
+  // Remote tiles go to slot `rank` of the owner's staging [ws][slab_rows][N]; own tiles go to `out`.
+  __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
+    const int owner = owner_of(p, tr);
+    const int row0 = tr * kBM - owner * p.slab_rows;
+    if (owner == p.rank) return TileDest{(char*)p.out, p.ldo, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[p.ws] : nullptr};
+    char* base = (char*)p.bufs[owner] + (size_t)p.rank * p.slab_rows * p.rows_c * 2;
+    return TileDest{base, (long long)p.rows_c, row0, tc * bn, p.slab_rows, p.rows_c, p.use_tma_store ? &p.tmap_out[owner] : nullptr};
+  }
+  // Own tiles: add the peers' staged partial sums (bf16) to the fp32 fragment, in rank order.
+  __device__ __forceinline__ void add_to_chunk(const GemmParams& p, int tr, int tc, int row_in_tile, int col_in_tile,
+                                               uint32_t (&r)[32], int n) {
+    if (owner_of(p, tr) != p.rank || p.ws == 1) return;
+    const int row = tr * kBM - p.rank * p.slab_rows + row_in_tile;
+    const int col = tc * bn + col_in_tile;
+    if (row >= p.slab_rows) return;
+    const char* stage = (const char*)p.bufs[p.rank];
+    const size_t slab_bytes = (size_t)p.slab_rows * p.rows_c * 2;
+    const size_t off = ((size_t)row * p.rows_c + col) * 2;
+    // Peers in batches of four: the 16 loads of a batch are issued before the first add, so a chunk
+    // costs ceil((ws-1)/4) memory round trips instead of ws-1. The order of the adds stays rank order.
+    for (int s0 = 0; s0 < p.ws; s0 += 4) {
+      U4 x[4][4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        if (s < p.ws && s != p.rank) {
+          const char* src = stage + (size_t)s * slab_bytes + off;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (u * 8 < n && col + u * 8 < p.rows_c) x[k][u] = ld16(src + u * 16);   // N % 8 == 0: units are all-in or all-out
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        if (s < p.ws && s != p.rank) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (u * 8 < n && col + u * 8 < p.rows_c) {
+              const uint32_t w[4] = {x[k][u].x, x[k][u].y, x[k][u].z, x[k][u].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                r[u * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e]) + bf16lo(w[e]));
+                r[u * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[u * 8 + 2 * e + 1]) + bf16hi(w[e]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
+    const int owner = owner_of(p, tr);
+    if (owner == p.rank) return true;
+    epi_bar_sync();   // all four epilogue warps have issued their stores of this tile
+    if (q == 0 && lane == 0) red_add_release_sys(p.pads[owner] + p.flag_base + local_tile(p, tr, tc), 1u);
+    return true;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// pull: every tile goes to the own staging matrix; reducer warps sum the tiles this rank owns
+// ---------------------------------------------------------------------------------------------
+struct RsPullHooks : HookDefaults {
+  int bn;
+  __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
+  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
+  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
+  __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
+    char* base = (char*)p.bufs[p.rank] + p.stage_off;
+    return TileDest{base, (long long)p.rows_c, tr * kBM, tc * bn, p.rows_r, p.rows_c, p.use_tma_store ? &p.tmap_out[0] : nullptr};
+  }
+  // counter of 128-row tile `tr`, column tile `tc` in its owner's signal pad
+  __device__ __forceinline__ uint32_t* counter(const GemmParams& p, int owner, int tr, int tc) const {
+    return p.pads[owner] + p.flag_base + (size_t)(tr - owner * (p.slab_rows / kBM)) * p.tiles_c + tc;
+  }
+  __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
+    if (tr * kBM >= p.rows_r) return true;
+    epi_bar_sync();   // all four epilogue warps' stores of this tile are complete
+    if (q == 0 && lane == 0) {
+      const int owner = (tr * kBM) / p.slab_rows;
+      red_add_release_sys(counter(p, owner, tr, tc), 1u);
+    }
+    return true;
+  }
+
+  // Sums 128-row tile (tr, tc) over all ranks into `out`. Thread tid of 128 handles 16-byte
+  // vectors tid, tid + 128, ...: a warp covers one 512-byte row segment per instruction.
+  __device__ __forceinline__ bool reduce_unit(const GemmParams& p, int tr, int tc, int tid) {
+    uint32_t* f = counter(p, p.rank, tr, tc);
+    const uint32_t need = (uint32_t)p.ws;
+    if (tid == 0)
+      spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 57, 0, blockIdx.x));
+    reducer_bar_sync();
+    if (!status_ok(p.sync)) return false;
+    const int N = p.rows_c;
+    const int col0 = tc * bn;
+    const int ncols = min(bn, N - col0);
+    const int vpr = ncols / 8;                       // N % 8 == 0
+    const int rows = min(kBM, p.rows_r - tr * kBM);
+    const int total = rows * vpr;
+    const size_t g_row0 = (size_t)tr * kBM;
+    const size_t o_row0 = g_row0 - (size_t)p.rank * p.slab_rows;
+    if (p.mc_ptr != nullptr) {
+      // in-switch sum: eight 16-byte multimem.ld_reduce in flight per thread
+      constexpr int B = 8;
+      for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * B) {
+        U4 x[B];
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          const int i = i0 + k * kRsReducerThreads;
+          if (i < total) {
+            const int r = i / vpr, v = i - r * vpr;
+            x[k] = multimem_ld_reduce_bf16x8((const char*)p.mc_ptr + p.stage_off + ((g_row0 + r) * N + col0 + v * 8) * 2);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          const int i = i0 + k * kRsReducerThreads;
+          if (i < total) {
+            const int r = i / vpr, v = i - r * vpr;
+            st16((char*)p.out + ((o_row0 + r) * p.ldo + col0 + v * 8) * 2, x[k]);
+          }
+        }
+      }
+    } else {
+      // peer loads: two vectors per thread with every rank's load in flight; adds in rank order
+      for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * 2) {
+        float f8[2][8];
+        size_t soff[2];
+        bool act[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int i = i0 + k * kRsReducerThreads;
+          act[k] = i < total;
+          const int r = act[k] ? i / vpr : 0, v = act[k] ? i - r * vpr : 0;
+          soff[k] = ((g_row0 + r) * N + col0 + v * 8) * 2;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f8[k][e] = 0.f;
+        }
+        for (int s0 = 0; s0 < p.ws; s0 += 8) {
+          U4 x[2][8];
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (act[k] && s0 + s < p.ws) x[k][s] = ld16((const char*)p.bufs[s0 + s] + p.stage_off + soff[k]);
+#pragma unroll
+          for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int s = 0; s < 8; ++s)
+              if (act[k] && s0 + s < p.ws) acc8(x[k][s], f8[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int i = i0 + k * kRsReducerThreads;
+          if (act[k]) {
+            const int r = i / vpr, v = i - r * vpr;
+            st16((char*)p.out + ((o_row0 + r) * p.ldo + col0 + v * 8) * 2, pack8(f8[k]));
+          }
+        }
+      }
+    }
+    // counter back to zero for the call after next (the next one uses the other bank)
+    if (tid == 0) red_add_relaxed_sys(f, 0u - need);
+    return true;
+  }
+
+  // Reducer warps: walk the tile order, count the tiles of the own slab and serve every
+  // num_workers-th of them (a CTA pair: each CTA its own 128-row half).
+  __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
+    const int total = p.tiles_r * p.tiles_c;
+    const int rows_per_tile = half < 0 ? kBM : 2 * kBM;
+    unsigned own = 0;
+    for (int t = 0; t < total; ++t) {
+      int trv, tc;
+      tile_coords(p, t, trv, tc);
+      if ((trv * rows_per_tile) / p.slab_rows != p.rank) continue;
+      const bool mine = (own % num_workers) == worker;
+      ++own;
+      if (!mine) continue;
+      const int tr = half < 0 ? trv : 2 * trv + half;
+      if (tr * kBM >= p.rows_r) continue;
+      if (!reduce_unit(p, tr, tc, tid)) return;
+    }
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// kernels: ALGO 0 push (192 threads), 1 pull (192 + 128 reducer threads)
+// ---------------------------------------------------------------------------------------------
+template <int ALGO>
+__device__ __forceinline__ void rs_body(const GemmParams& p, unsigned bid, unsigned nb) {
+  extern __shared__ unsigned char smem_raw[];
+  if (ALGO == 0) {
+    RsPushHooks h;
+    h.bn = 256;
+    gemm_mainloop<256>(p, bid, nb, h, smem_raw);
+    // staging slabs and flags may be reused by the next launch only after every rank is done
+    symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
+  } else {
+    RsPullHooks h;
+    h.bn = 256;
+    gemm_mainloop<256>(p, bid, nb, h, smem_raw);
+  }
+}
+template <int ALGO>
+__device__ __forceinline__ void rs_pair_body(const GemmParams& p, unsigned bid, unsigned nb) {
+  extern __shared__ unsigned char smem_raw[];
+  if (ALGO == 0) {
+    RsPushHooks h;
+    h.bn = 256;
+    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
+    symm_mem_sync<true, false>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 56);
+  } else {
+    RsPullHooks h;
+    h.bn = 256;
+    gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_rs_push_kernel(const __grid_constant__ GemmParams p) {
+  rs_body<0>(p, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_rs_push_emu_kernel(const GemmParams* ps) {
+  rs_body<0>(ps[blockIdx.y], blockIdx.x, gridDim.x);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_rs_push_pair_kernel(const __grid_constant__ GemmParams p) {
+  rs_pair_body<0>(p, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(kRsPullThreads, 1) gemm_rs_pull_kernel(const __grid_constant__ GemmParams p) {
+  rs_body<1>(p, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(kRsPullThreads, 1) gemm_rs_pull_emu_kernel(const GemmParams* ps) {
+  rs_body<1>(ps[blockIdx.y], blockIdx.x, gridDim.x);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kRsPullThreads, 1)
+    gemm_rs_pull_pair_kernel(const __grid_constant__ GemmParams p) {
+  rs_pair_body<1>(p, blockIdx.x, gridDim.x);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host
+// ---------------------------------------------------------------------------------------------
+struct RsPlan {
+  int pair;            // 1: CTA-pair kernel with 256 x 256 tiles, 0: single-CTA kernel with 128 x 256 tiles
+  int tiles_r, tiles_c;
+  int group_r, pivot_r, interleave_r;
+  int workers;         // CTA pairs (pair) or CTAs that walk the tile order
+  int grid;            // CTAs launched
+};
+
+// Tiling and tile order of the fused reduce-scatter GEMM; one function for the launcher and for
+// the host-side model of the flag protocol used by the tests.
+static int rs_plan(int M, int N, int ws, int rank, int algo, unsigned cap, bool allow_pair, RsPlan* pl) {
+  KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
+  KR_REQUIRE(M % ws == 0 && (M / ws) % kBM == 0, "fused GEMM reduce-scatter needs (M / world_size) % 128 == 0");
+  KR_REQUIRE(N >= 256 && N % 8 == 0, "fused GEMM reduce-scatter needs N >= 256 and N % 8 == 0");
+  KR_REQUIRE(cap >= 1, "no CTAs");
+  const int slab_rows = M / ws;
+  pl->pair = allow_pair && cap >= 2 && (slab_rows % 256) == 0 ? 1 : 0;
+  const int rows_per_tile = pl->pair ? 256 : kBM;
+  const int per_slab = slab_rows / rows_per_tile;
+  pl->tiles_r = M / rows_per_tile;
+  pl->tiles_c = (N + 255) / 256;
+  int g = default_group_r();                    // counted in 128-row tiles
+  if (pl->pair) g = g >= 2 ? g / 2 : 1;
+  if (algo == 0) {
+    // next rank's slab first, own slab last; groups never straddle two slabs
+    pl->pivot_r = (((rank + 1) % ws) * per_slab) % pl->tiles_r;
+    pl->interleave_r = 0;
+    if (g > per_slab) g = per_slab;
+    while (per_slab % g) --g;
+  } else {
+    // the same order on every rank, owners interleaved
+    pl->pivot_r = 0;
+    pl->interleave_r = ws;
+    if (g > pl->tiles_r) g = pl->tiles_r;
+  }
+  pl->group_r = g;
+  const unsigned tiles = (unsigned)pl->tiles_r * (unsigned)pl->tiles_c;
+  if (pl->pair) {
+    unsigned pairs = tiles < cap / 2 ? tiles : cap / 2;
+    pl->workers = (int)pairs;
+    pl->grid = (int)(2 * pairs);
+  } else {
+    unsigned n = tiles < cap ? tiles : cap;
+    pl->workers = (int)n;
+    pl->grid = (int)n;
+  }
+  return KR_SUCCESS;
+}
+
+}  // namespace kraken
+
+using namespace kraken;
+
+// out[0..7] = {pair, tiles_r, tiles_c, group_r, pivot_r, interleave_r, workers, grid} for the
+// given problem on a device with `num_ctas` CTAs available. For tests of the flag protocol.
+KR_API int kr_rs_plan(int M, int N, int ws, int rank, int algo, int num_ctas, int allow_pair, int* out) {
+  RsPlan pl;
+  int rc = rs_plan(M, N, ws, rank, algo, (unsigned)num_ctas, allow_pair != 0, &pl);
+  if (rc) return rc;
+  out[0] = pl.pair; out[1] = pl.tiles_r; out[2] = pl.tiles_c; out[3] = pl.group_r;
+  out[4] = pl.pivot_r; out[5] = pl.interleave_r; out[6] = pl.workers; out[7] = pl.grid;
+  return KR_SUCCESS;
+}
+
+// Fused GEMM -> reduce-scatter. a[M, K_local], bt[N, K_local]; out[M/ws, N] bf16.
+// bufs[r] = rank r's staging workspace (bufs: device table; bufs_host: the same addresses in host
+// memory, used to describe staging to TMA, or nullptr): push needs M*N*2 bytes, pull 2*M*N*2
+// (two halves, alternating with call_parity) and DEDICATED to this op. mc_ptr: multicast address of
+// the staging workspace or nullptr (pull then sums with peer loads). algo: 0 push, 1 pull.
+// Tile counters live in the signal pads from word flag_base on (zero on entry, zero again after
+// the call); pull uses the bank selected by call_parity.
+KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads, void* mc_ptr, int rank,
+                           int ws, const void* a, long long lda, const void* bt, long long ldb, void* out,
+                           long long ldo, int M, int N, int K, int algo, int call_parity, uint32_t pad_base,
+                           uint32_t flag_base, unsigned long long pad_words, unsigned long long staging_bytes,
+                           cudaStream_t stream) {
+  DeviceState* d = device_state();
+  if (!d) return KR_FAIL_CUDA;
+  KR_REQUIRE(algo == 0 || algo == 1, "algo must be 0 (push) or 1 (pull)");
+  KR_REQUIRE(pad_base % (ws > 0 ? ws : 1) == 0, "pad_base must be a multiple of the world size");
+  KR_REQUIRE(ldo % 8 == 0 && ((uintptr_t)out & 15) == 0, "output rows must be 16-byte aligned");
+  const unsigned cap = grid_cap(d);
+  RsPlan pl;
+  int rc = rs_plan(M, N, ws, rank, algo, cap, pair_enabled() && !emu_recorder().active, &pl);
+  if (rc) return rc;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  int bn = 0;
+  rc = setup_problem(p, a, lda, bt, ldb, M, N, K, false, 256, &bn);
+  if (rc) return rc;
+  p.mode = GEMM_RS;
+  p.rs_algo = algo;
+  p.out = out;
+  p.ldo = ldo;
+  p.out_rows = M / ws;
+  p.out_cols = N;
+  p.rank = rank;
+  p.ws = ws;
+  p.bufs = bufs;
+  p.pads = pads;
+  p.pad_base = pad_base;
+  p.slab_rows = M / ws;
+  p.sync = sync_ctx(d);
+  const unsigned long long mn2 = (unsigned long long)M * N * 2;
+  const unsigned long long units = (unsigned long long)(p.slab_rows / kBM) * pl.tiles_c;
+  if (algo == 0) {
+    KR_REQUIRE(staging_bytes >= mn2, "staging workspace too small");
+    KR_REQUIRE((unsigned long long)flag_base + units <= pad_words, "signal pad too small for the tile flags");
+    KR_REQUIRE((unsigned long long)pad_base + (unsigned long long)cap * ws <= flag_base, "barrier slots overlap tile flags");
+    p.flag_base = flag_base;
+    // TMA-store destinations: rank o's staging slot [rank] for every o, and the local output.
+    if (bufs_host != nullptr && ws <= 8) {
+      bool ok = store_tmap(out, p.slab_rows, N, ldo, &p.tmap_out[ws]);
+      for (int o = 0; o < ws && ok; ++o)
+        ok = store_tmap((const char*)bufs_host[o] + (size_t)rank * p.slab_rows * N * 2, p.slab_rows, N, N, &p.tmap_out[o]);
+      p.use_tma_store = ok ? 1 : 0;
+    }
+  } else {
+    const unsigned long long half = staging_bytes / 2 / 1024 * 1024;
+    KR_REQUIRE(half >= mn2, "staging workspace too small (pull needs 2 * M * N * 2 bytes)");
+    const unsigned long long bank = (pad_words - flag_base) / 2;
+    KR_REQUIRE(pad_words > flag_base && units <= bank, "signal pad too small for the tile counters");
+    p.stage_off = (call_parity & 1) ? half : 0;
+    p.flag_base = flag_base + ((call_parity & 1) ? (uint32_t)bank : 0u);
+    p.mc_ptr = mc_ptr;
+    if (bufs_host != nullptr)
+      p.use_tma_store = store_tmap((const char*)bufs_host[rank] + p.stage_off, M, N, N, &p.tmap_out[0]) ? 1 : 0;
+  }
+  p.tiles_r = pl.tiles_r;
+  p.tiles_c = pl.tiles_c;
+  p.group_r = pl.group_r;
+  p.pivot_r = pl.pivot_r;
+  p.interleave_r = pl.interleave_r;
+  p.num_mma_ctas = pl.grid;
+  const unsigned threads = algo == 0 ? kGemmThreads : kRsPullThreads;
+  if (pl.pair) {
+    // each CTA of a pair loads its own 128 rows of the column operand: box of 128 rows, not 256
+    rc = get_tmap(p.host_c_ptr, p.rows_c, p.K, p.host_ldc, 128, &p.tmap_c);
+    if (rc) return rc;
+    const void* fn = algo == 0 ? (const void*)gemm_rs_push_pair_kernel : (const void*)gemm_rs_pull_pair_kernel;
+    rc = ensure_dynamic_smem(fn, PairCfg::SMEM);
+    if (rc) return rc;
+    void* args[] = {(void*)&p};
+    KR_CUDA(cudaLaunchKernel(fn, dim3((unsigned)pl.grid), dim3(threads), args, PairCfg::SMEM, stream));
+    return KR_SUCCESS;
+  }
+  if (algo == 0)
+    return launch_ranked(gemm_rs_push_kernel, gemm_rs_push_emu_kernel, p, (unsigned)pl.grid, threads, GemmCfg<256>::SMEM, stream);
+  return launch_ranked(gemm_rs_pull_kernel, gemm_rs_pull_emu_kernel, p, (unsigned)pl.grid, threads, GemmCfg<256>::SMEM, stream);
+}

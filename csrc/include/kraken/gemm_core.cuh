@@ -13,6 +13,8 @@
 //   warps 2-5  epilogue: tcgen05.ld the finished accumulator, convert, stage through shared
 //              memory and write coalesced rows to local or PEER memory, while warp 1 already
 //              runs the next tile's main loop into the other accumulator.
+//   warps 6+   (only in kernels launched with more than 192 threads) a side role supplied by the
+//              hooks, e.g. the reducer warps of the GEMM -> reduce-scatter kernel
 // The reference's main loops are tl.dot recipes (kraken/fused/all_gather_matmul.py:25-123,
 // kraken/fused/gemm_reduce_scatter_ce_persistent.py:46-134,
 // kraken/fused/gemm_one_shot_all_reduce_fused.py:10-103); nothing of their structure is reused.
@@ -52,6 +54,7 @@ struct alignas(64) GemmParams {
   int tiles_r, tiles_c;      // tile counts
   int group_r;               // consecutive row-tiles sharing column sweeps (L2 reuse)
   int pivot_r;               // row-tile rotation (rank pivot)
+  int interleave_r;          // > 1: row tiles are dealt round-robin over this many equal slabs
   int mode;
   int transposed;            // 1: D tile is C^T (store element (i,j) at out[j][i])
   int out_fp32;              // 1: fp32 output, 0: bf16
@@ -84,6 +87,7 @@ struct alignas(64) GemmParams {
   void* mc_ptr;                   // multicast address of the staging buffer (NVLS) or nullptr
   // RS
   int slab_rows;             // M / ws
+  int rs_algo;               // 0: push partial tiles to the owner; 1: owner pulls and reduces (NVLS or peer loads)
   SyncCtx sync;
   // host-side bookkeeping (not read on the device): the column operand as given, so that a
   // launcher can re-encode its tensor map with another box height
@@ -104,6 +108,9 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int t,
   tc = in / gsz;
   tr += p.pivot_r;
   if (tr >= p.tiles_r) tr -= p.tiles_r;
+  // Interleaved slabs: consecutive row tiles of the order belong to consecutive slabs (owners), so
+  // every owner's tiles finish at an even rate instead of slab after slab.
+  if (p.interleave_r > 1) tr = (tr % p.interleave_r) * (p.tiles_r / p.interleave_r) + tr / p.interleave_r;
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -113,7 +120,17 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 //   map to read it from and may rewrite the row coordinate; false aborts.
 //   Epilogue hooks: begin_tile (may wait for peers' data), tile_dest (where tile (tr, tc) is
 //   stored), add_to_chunk (adds other ranks' partial sums to a row fragment still in registers;
-//   row-major path only), after_store (what happens once the tile is stored).
+//   row-major path only), after_store (what happens once the tile is stored), may_wait (whether
+//   begin_tile of that row tile can block on another rank: the main loop then first runs any
+//   completion hook it still holds back, so that no rank waits while it withholds a signal),
+//   side_role (work of the warps beyond the six pipeline warps, if the launch has any).
+struct HookDefaults {
+  __device__ __forceinline__ bool may_wait(const GemmParams&, int) const { return false; }
+  // worker / num_workers: this CTA (or CTA pair) among those of the launch; half: -1 for a single
+  // CTA, else the CTA's rank inside its pair; tid: thread index among the side-role warps.
+  __device__ __forceinline__ void side_role(const GemmParams&, unsigned, unsigned, int, int) {}
+};
+
 struct TileDest {
   char* base;        // address of element (0,0) of the destination matrix
   long long ld;      // elements per destination row
@@ -396,6 +413,8 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
         if (ok) umma_commit(tfull_bar(acc));   // accumulator complete
       }
     }
+  } else if (warp >= 6) {
+    hooks.side_role(p, bid, nb, -1, (int)threadIdx.x - kGemmThreads);
   } else {
     // ================= epilogue warps =================
     const int q = warp & 3;                                  // TMEM lane quarter this warp may read
@@ -414,6 +433,17 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (defer && prev_tr >= 0 && hooks.may_wait(p, tr)) {
+        // never block on a peer while a finished tile's signal is still held back
+        if (lane == 0) {
+          bulk_wait_group<0>();
+          fence_proxy_async();
+        }
+        __syncwarp();
+        ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
+        prev_tr = -1;
+        if (!ok) break;
+      }
       ok = gemm_epilogue_tile<BN, false>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, tempty_bar(acc), defer);
       if (!ok) break;
       if (defer) {
@@ -579,6 +609,8 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
         }
       }
     }
+  } else if (warp >= 6) {
+    hooks.side_role(p, pair_id, num_pairs, (int)cta, (int)threadIdx.x - kGemmThreads);
   } else {
     // ================= epilogue warps (both CTAs, own 128 rows) =================
     const int q = warp & 3;
@@ -598,6 +630,16 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (defer && prev_tr >= 0 && hooks.may_wait(p, tr)) {
+        if (lane == 0) {
+          bulk_wait_group<0>();
+          fence_proxy_async();
+        }
+        __syncwarp();
+        ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
+        prev_tr = -1;
+        if (!ok) break;
+      }
       ok = gemm_epilogue_tile<Cfg::BN, true>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, lead_tempty[acc], defer);
       if (!ok) break;
       if (defer) {

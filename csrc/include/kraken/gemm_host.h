@@ -1,0 +1,22 @@
+// Host-side helpers shared by the GEMM translation units: the tensor-map cache, tiling defaults
+// and the operand set-up of C[M,N] = A[M,K] * Bt[N,K]^T. Defined in gemm.cu.
+#pragma once
+#include "kraken/driver_api.h"
+#include "kraken/gemm_core.cuh"
+
+namespace kraken {
+
+// Tensor map of a row-major bf16 matrix [rows, cols] (cols contiguous, `ld` elements per row),
+// box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range elements read as zero. Cached.
+int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+             unsigned box_rows, CUtensorMap* out);
+// Tensor map for TMA stores of bf16 tiles (box of 32 rows); false when the matrix cannot be
+// described to TMA or TMA stores are switched off.
+bool store_tmap(const void* ptr, long long rows, long long cols, long long ld, CUtensorMap* m);
+int default_group_r();
+bool pair_enabled();
+unsigned grid_cap(const DeviceState* d);
+int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, long long ldb, int M, int N, int K,
+                  bool swap, int bn_override, int* bn_out);
+
+}  // namespace kraken

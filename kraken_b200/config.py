@@ -13,6 +13,8 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_TMA_STORE``        ``0`` makes the GEMM epilogue use vector stores instead of TMA stores
 ``KRAKEN_AG_MODE``          ``ce`` (copy engines + stream flags feed the GEMM kernel, default) or ``sm`` (comm CTAs
                             inside the GEMM kernel pull the shards)
+``KRAKEN_RS_ALGO``          ``pull`` (default: owners sum the ranks' staged tiles, in the NVSwitch when possible) or
+                            ``push`` (partial tiles are pushed to the owner and summed in its epilogue)
 ``KRAKEN_NVTX``             ``1`` wraps every public op in an NVTX range named after it (for timeline tools)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
@@ -59,6 +61,11 @@ def num_comm_sms() -> int:
 def ag_mode() -> str:
     v = os.environ.get("KRAKEN_AG_MODE", "ce").strip().lower()
     return v if v in ("sm", "ce") else "ce"
+
+
+def rs_algo() -> str:
+    v = os.environ.get("KRAKEN_RS_ALGO", "pull").strip().lower()
+    return v if v in ("pull", "push") else "pull"
 
 
 def dump_kernel() -> bool:

@@ -16,6 +16,7 @@ import torch
 
 from .. import _reference as ref
 from .. import config
+from .._logging import utils as _log
 from ..ops import lib as _lib
 from ..parallel import symm_mem
 from .gemm_common import as_k_major_a, as_k_major_bt
@@ -119,8 +120,7 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     backend = kwargs.get("backend", config.ag_mode())
     counters = _zero_counters(a_shared.device, ws * splits, hdl.group.emu)
     L = _lib.lib()
-    if config.dump_kernel() and rank == 0:
-        print(f"[kraken_b200] all_gather_matmul M={M} N={N} K={K} ws={ws} splits={splits} engine={backend}", flush=True)
+    _log.log_kernel_choice("all_gather_matmul", f"M={M} N={N} K={K} ws={ws} splits={splits} engine={backend}")
     off = hdl.offset_of(a_shared)
     if off:
         raise ValueError("a_shared must start at the beginning of its symmetric buffer")
@@ -185,12 +185,15 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
 
 
 def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
-    """[M/ws, N] = reduce_scatter(a @ b) along M, in one kernel. Tile order: the next rank's slab
-    first, the own slab last. The epilogue TMA-stores every remote tile into its owner's staging
-    slab over NVLink and bumps the owner's per-tile flag; for own tiles it waits for the flag, adds
-    the peers' staged partial sums to the accumulator in rank order (bit-reproducible) and writes
-    the final rows. Shapes whose slab is not a multiple of 128 rows run GEMM -> symmetric staging
-    -> reduce-scatter kernel."""
+    """[M/ws, N] = reduce_scatter(a @ b) along M, in one kernel. Two exchange algorithms:
+    "pull" (default) — every rank TMA-stores its partial tiles into its own symmetric staging and
+    bumps a per-tile counter at the tile's owner; reducer warps inside the same kernel sum each owned
+    tile over all ranks (``multimem.ld_reduce`` in the NVSwitch, or peer loads in rank order) as soon
+    as all ranks have stored it, while the MMAs of later tiles run; "push" — the epilogue TMA-stores
+    remote tiles into the owner's staging slab over NVLink and the owner adds them to its accumulator
+    in the epilogue of its own tiles (computed last). Both are bit-reproducible from call to call.
+    Shapes whose slab is not a multiple of 128 rows, or N < 256, run GEMM -> symmetric staging ->
+    reduce-scatter kernel. kwargs: group, algo="pull"|"push" (default KRAKEN_RS_ALGO)."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_reduce_scatter(a, b, group)
@@ -204,22 +207,32 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
     ws = info.world_size
     if M % ws:
         raise ValueError("M must be divisible by the world size")
-    out_dtype = a.dtype if a.dtype in (torch.bfloat16,) else torch.bfloat16
-    out = torch.empty((M // ws, N), dtype=out_dtype, device=a.device)
-    if config.dump_kernel() and info.rank == 0:
-        path = "plain GEMM" if ws == 1 else ("fused epilogue push" if (M // ws) % 128 == 0 and N % 8 == 0
-                                             else "GEMM + reduce-scatter kernel")
-        print(f"[kraken_b200] gemm_reduce_scatter M={M} N={N} K={K} ws={ws}: {path}", flush=True)
+    out = torch.empty((M // ws, N), dtype=torch.bfloat16, device=a.device)
+    algo = str(kwargs.get("algo", config.rs_algo()))
+    if algo not in ("pull", "push"):
+        raise ValueError("algo must be 'pull' or 'push'")
+    fused_ok = (M // ws) % 128 == 0 and N % 8 == 0 and N >= 256
+    force = bool(kwargs.get("_force_fused", False))           # tests: run the fused kernel at world size 1
+    if _log.dump_enabled():
+        path = "plain GEMM" if ws == 1 and not force else (f"fused, {algo}" if fused_ok
+                                                           else "GEMM + reduce-scatter kernel")
+        _log.log_kernel_choice("gemm_reduce_scatter", f"M={M} N={N} K={K} ws={ws}: {path}")
     L = _lib.lib()
     s = _lib.current_stream_ptr()
-    if ws == 1:
+    if ws == 1 and not (force and fused_ok):
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, s))
-    elif (M // ws) % 128 == 0 and N % 8 == 0:
-        hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
-        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev, hdl.rank, ws,
-                                     a2.data_ptr(), lda,
-                                     bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, config.TILE_FLAG_BASE,
-                                     hdl.signal_pad_words, s))
+    elif fused_ok:
+        if algo == "pull":
+            hdl = symm_mem.get_symm_mem_workspace(group, 2 * M * N * 2 + 2048, a.device, kind="gemm_rs")
+            calls = getattr(hdl, "_gemm_rs_calls", 0)        # per staging buffer: selects the half / counter bank
+            hdl._gemm_rs_calls = calls + 1
+        else:
+            hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
+            calls = 0
+        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev,
+                                     hdl.multicast_ptr or None, hdl.rank, ws, a2.data_ptr(), lda, bt.data_ptr(), ldb,
+                                     out.data_ptr(), N, M, N, K, 1 if algo == "pull" else 0, calls & 1, 0,
+                                     config.TILE_FLAG_BASE, hdl.signal_pad_words, hdl.buffer_size, s))
     else:
         if (M * N) % (8 * ws):
             raise ValueError("M * N must be a multiple of 8 * world size")
@@ -228,7 +241,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, 1, s))
         _lib.check(L.kr_reduce_scatter(hdl.buffer_ptrs_dev, 0, hdl.signal_pad_ptrs_dev, hdl.rank, ws, None,
                                        out.data_ptr(), M * N, 0, 0, s))
-    return out if out.dtype == a.dtype or a.dtype != torch.float32 else out.to(a.dtype)
+    return out if a.dtype != torch.float32 else out.to(a.dtype)
 
 
 _ce_state: dict[int, tuple] = {}

@@ -89,13 +89,14 @@ _PROTOS = {
                              c_int, c_int, _P]),
     "kr_ag_gemm_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int,
                                 c_int, _P, _P, c_int, c_uint32, _P]),
-    "kr_gemm_rs_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
-                                c_int, c_uint32, c_uint32, c_ulonglong, _P]),
+    "kr_gemm_rs_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
+                                c_int, c_int, c_int, c_uint32, c_uint32, c_ulonglong, c_ulonglong, _P]),
+    "kr_rs_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "kr_gemm_ar_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_uint32, c_ulonglong, c_ulonglong, _P]),
     "kr_gemm_ce_producer_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int,
                                          c_int, _P, _P, _P]),
-    "kr_tile_order": (c_int, [c_int, c_int, c_int, c_int, _P]),
+    "kr_tile_order": (c_int, [c_int, c_int, c_int, c_int, c_int, _P]),
     "kr_reduce_slabs": (c_int, [_P, _P, c_int, c_int, c_ulonglong, _P]),
 }
 

@@ -8,9 +8,9 @@ import pytest
 from kraken_b200.ops import lib as klib
 
 
-def _order(tiles_r, tiles_c, group_r, pivot_r):
+def _order(tiles_r, tiles_c, group_r, pivot_r, interleave_r=0):
     buf = (ctypes.c_int * (2 * tiles_r * tiles_c))()
-    klib.check(klib.lib().kr_tile_order(tiles_r, tiles_c, group_r, pivot_r, buf))
+    klib.check(klib.lib().kr_tile_order(tiles_r, tiles_c, group_r, pivot_r, interleave_r, buf))
     return [(buf[2 * i], buf[2 * i + 1]) for i in range(tiles_r * tiles_c)]
 
 
@@ -45,3 +45,13 @@ def test_all_gather_order_starts_on_the_local_shard(ws, rank):
     # then the shards in the order the all-gather delivers them: rank+1, rank+2, ...
     nxt = order[tiles_per_shard * tiles_c: 2 * tiles_per_shard * tiles_c]
     assert {r // tiles_per_shard for r, _ in nxt} == {(rank + 1) % ws}
+
+
+@pytest.mark.parametrize("tiles_r,tiles_c,group_r,il", [(8, 3, 8, 8), (32, 32, 8, 8), (32, 5, 8, 4), (16, 7, 8, 2), (12, 4, 8, 3)])
+def test_interleaved_slabs_every_tile_once_and_owners_rotate(tiles_r, tiles_c, group_r, il):
+    order = _order(tiles_r, tiles_c, group_r, 0, il)
+    assert sorted(order) == [(r, c) for r in range(tiles_r) for c in range(tiles_c)]
+    per_slab = tiles_r // il
+    # the first `il` tiles of the order hit `il` different slabs when a group holds at least `il` rows
+    if group_r >= il:
+        assert {r // per_slab for r, _ in order[:il]} == set(range(il))

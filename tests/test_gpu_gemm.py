@@ -131,18 +131,52 @@ def test_all_gather_matmul(ws, splits):
             assert bool((progs[r].to(torch.int64) != 0).all())
 
 
-@pytest.mark.parametrize("ws", [2, 4])
-def test_gemm_reduce_scatter_fused(ws):
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("algo", ["pull", "push"])
+def test_gemm_reduce_scatter_fused(ws, algo):
     world = EmuWorld(ws)
     M, N, Kl = 128 * ws * 2, 512, 256
     g = torch.Generator().manual_seed(7)
     a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
     bt_s = [(0.05 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
     full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
-    for _ in range(2):     # second round: staging and tile flags reused
-        outs = world.run(lambda r: fused.gemm_reduce_scatter(a_s[r], bt_s[r].t()))
+    for _ in range(3):     # staging halves / counter banks alternate, then the first is reused
+        outs = world.run(lambda r: fused.gemm_reduce_scatter(a_s[r], bt_s[r].t(), algo=algo))
         for r in range(ws):
             torch.testing.assert_close(outs[r].float(), full[r * (M // ws):(r + 1) * (M // ws)], atol=6e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("algo", ["pull", "push"])
+def test_gemm_reduce_scatter_fused_several_tiles_per_cta(algo):
+    # 4 ranks x 37 CTAs, 16 x 5 tiles of 128 x 256 (last column tile ragged): every CTA walks two or
+    # three tiles, owners interleaved (pull) or slab after slab (push)
+    ws = 4
+    world = EmuWorld(ws)
+    M, N, Kl = 2048, 1160, 128
+    g = torch.Generator().manual_seed(17)
+    a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+    bt_s = [(0.05 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
+    full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
+    first = None
+    for _ in range(2):
+        outs = world.run(lambda r: fused.gemm_reduce_scatter(a_s[r], bt_s[r].t(), algo=algo))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r].float(), full[r * (M // ws):(r + 1) * (M // ws)], atol=6e-2, rtol=3e-2)
+        if first is None:
+            first = [o.clone() for o in outs]
+        else:
+            assert all(torch.equal(x, y) for x, y in zip(first, outs))      # bit-reproducible
+
+
+@pytest.mark.parametrize("algo", ["pull", "push"])
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 512), (4096, 1032, 256), (512, 256, 64)])
+def test_gemm_reduce_scatter_kernel_at_world_size_one(algo, M, N, K):
+    # the fused kernels (CTA pairs, reducer warps, counters, staging halves) on one real rank
+    a, bt = _ab(M, N, K, seed=18)
+    ref = a.float() @ bt.float().t()
+    for _ in range(3):
+        c = fused.gemm_reduce_scatter(a, bt.t(), algo=algo, _force_fused=True)
+        _close(c, ref, K)
 
 
 @pytest.mark.parametrize("ws", [2, 4])
