@@ -588,11 +588,13 @@ static int noalloc_device(NoAllocDevice** out) {
   return KR_SUCCESS;
 }
 
+static uint64_t g_noalloc_timeout_ns = 0;   // 0: follow the device's setting (or the environment default)
+
+// Deadline of the waits in the allocation-free path: its own setting if one was made, else the
+// current device's (when other entry points have created that state), else the environment default.
 static uint64_t noalloc_timeout_ns() {
-  const char* e = getenv("KRAKEN_SYNC_TIMEOUT_MS");
-  double ms = e ? atof(e) : 4000.0;
-  if (ms <= 0) ms = 4000.0;
-  return (uint64_t)(ms * 1e6);
+  if (g_noalloc_timeout_ns != 0) return g_noalloc_timeout_ns;
+  return current_timeout_ns();
 }
 }  // namespace kraken
 
@@ -614,9 +616,22 @@ KR_API int kr_all_gather_sm_noalloc(void* const* bufs, unsigned long long buf_of
   NoAllocDevice* d = nullptr;
   int rc = noalloc_device(&d);
   if (rc) return rc;
+  // The scratch address belongs to the current device: a stream of another device would run the
+  // kernel there, against memory it was not meant for.
+  int stream_dev = -1, cur_dev = -1;
+  KR_CUDA(cudaGetDevice(&cur_dev));
+  if (cudaStreamGetDevice(stream, &stream_dev) == cudaSuccess)
+    KR_REQUIRE(stream_dev == cur_dev, "kr_all_gather_sm_noalloc: the stream belongs to another device than the current one");
+  else
+    (void)cudaGetLastError();
   uint32_t* counters = d->scratch + kNoAllocStatusWords;
-  // the array keeps whatever the previous call left: counters must start at zero
-  KR_CUDA(cudaMemsetAsync(counters, 0, sizeof(uint32_t) * (size_t)ws * splits, stream));
+  // The array keeps whatever the previous call left. The counters must start at zero; so must the
+  // built-in status word when this call uses it (a code left there would make every wait give up).
+  if (status == nullptr) {
+    KR_CUDA(cudaMemsetAsync(d->scratch, 0, sizeof(uint32_t) * ((size_t)kNoAllocStatusWords + (size_t)ws * splits), stream));
+  } else {
+    KR_CUDA(cudaMemsetAsync(counters, 0, sizeof(uint32_t) * (size_t)ws * splits, stream));
+  }
   CommParams p;
   memset(&p, 0, sizeof(p));
   p.bufs = bufs;
@@ -639,5 +654,26 @@ KR_API int kr_all_gather_sm_noalloc(void* const* bufs, unsigned long long buf_of
   if (nb > cap) nb = cap;
   void* args[] = {(void*)&p};
   KR_CUDA(cudaLaunchKernel((const void*)all_gather_kernel, dim3(nb), dim3(kCommThreads), args, 0, stream));
+  return KR_SUCCESS;
+}
+
+// Reads the built-in status word of the current device (the one calls with status == NULL use)
+// after synchronising `stream`; clear != 0 also zeroes it. No allocation.
+KR_API int kr_noalloc_read_status(cudaStream_t stream, uint32_t* word, int clear) {
+  KR_REQUIRE(word != nullptr, "null argument");
+  NoAllocDevice* d = nullptr;
+  int rc = noalloc_device(&d);
+  if (rc) return rc;
+  KR_CUDA(cudaStreamSynchronize(stream));
+  KR_CUDA(cudaMemcpy(word, d->scratch, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (clear) KR_CUDA(cudaMemset(d->scratch, 0, sizeof(uint32_t)));
+  return KR_SUCCESS;
+}
+
+// Deadline of the device-side waits of kr_all_gather_sm_noalloc, in milliseconds; 0 restores the
+// default (the current device's kr_set_timeout_ms value, else KRAKEN_SYNC_TIMEOUT_MS, else 4000).
+KR_API int kr_noalloc_set_timeout_ms(double ms) {
+  KR_REQUIRE(ms >= 0, "timeout must not be negative");
+  g_noalloc_timeout_ns = (uint64_t)(ms * 1e6);
   return KR_SUCCESS;
 }

@@ -43,6 +43,8 @@ struct DeviceState {
 
 // State of the CURRENT device (created on first use). Returns nullptr after setting the error.
 DeviceState* device_state();
+// Deadline of device-side waits on the current device; never allocates.
+uint64_t current_timeout_ns();
 inline SyncCtx sync_ctx(const DeviceState* d) { return SyncCtx{d->status, d->timeout_ns}; }
 
 // ---- rank emulation ---------------------------------------------------------------------------

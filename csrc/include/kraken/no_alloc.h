@@ -14,9 +14,19 @@
  *     for the life of the process.
  *   - The first call on each device looks up the scratch address (a host-side query, no
  *     allocation). Make that first call outside of any stream capture.
- *   - All calls on one device share the scratch. The counters are cleared on `stream` at the start
- *     of every call, so two calls whose kernels can overlap on the GPU (different streams) race;
- *     issue them on one stream or order them with events.
+ *   - All calls on one device share the scratch. The counters (and, for calls that pass
+ *     status == NULL, the built-in status word) are cleared on `stream` at the start of every
+ *     call, so two calls whose kernels can overlap on the GPU (different streams) race; issue them
+ *     on one stream or order them with events.
+ *   - `stream` must belong to the current device (the scratch address is per device); a stream of
+ *     another device is rejected.
+ *   - Failure reporting. Every device-side wait has a deadline (kr_noalloc_set_timeout_ms; default:
+ *     the library-wide setting). When one expires the kernel writes a non-zero code to the status
+ *     word, copies nothing more and returns; the host call has long returned 0 by then. A status
+ *     word the caller passes must be zero on entry and is the caller's to read and to clear. With
+ *     status == NULL the code goes to the built-in word: read it with kr_noalloc_read_status()
+ *     after the call you want to check — the next call with status == NULL starts by clearing it,
+ *     so a past timeout neither lingers nor makes later calls give up.
  *   - No cudaMalloc / cudaFree / allocating library routine is called. Inputs and outputs —
  *     including the pointer tables `bufs` and `pads`, `output`, `progress` and the optional
  *     `status` word — are the caller's memory.
@@ -42,6 +52,15 @@ int kr_all_gather_sm_noalloc(void* const* bufs, unsigned long long buf_off, uint
                              int world_size, void* output, uint32_t* progress, int splits,
                              unsigned long long numel, int max_blocks, uint32_t pad_base, uint32_t* status,
                              cudaStream_t stream);
+
+/* Synchronises `stream`, then stores the built-in status word of the current device in *word
+ * (0 = no wait gave up); clear != 0 also zeroes it. Allocates nothing. */
+int kr_noalloc_read_status(cudaStream_t stream, uint32_t* word, int clear);
+
+/* Deadline, in milliseconds, of the device-side waits of kr_all_gather_sm_noalloc; 0 restores the
+ * default (the value of kr_set_timeout_ms for the current device if that was ever called, else
+ * KRAKEN_SYNC_TIMEOUT_MS, else 4000 ms). Allocates nothing. */
+int kr_noalloc_set_timeout_ms(double ms);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,17 @@ DeviceState* device_state() {
   return d;
 }
 
+// Wait deadline that applies on the current device, found without creating (allocating) its state.
+uint64_t current_timeout_ns() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_states.find(dev);
+    if (it != g_states.end()) return it->second->timeout_ns;
+  }
+  return default_timeout_ns();
+}
+
 int ensure_dynamic_smem(const void* func, size_t smem) {
   static std::map<std::pair<int, const void*>, size_t> done;
   int dev = 0;

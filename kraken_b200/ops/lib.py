@@ -74,6 +74,8 @@ _PROTOS = {
     "kr_all_gather_sm": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, _P, c_int, c_ulonglong, c_int, c_uint32, _P]),
     "kr_all_gather_sm_noalloc": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, c_int, c_ulonglong, c_int, c_uint32,
                                          _P, _P]),
+    "kr_noalloc_read_status": (c_int, [_P, POINTER(c_uint32), c_int]),
+    "kr_noalloc_set_timeout_ms": (c_int, [c_double]),
     "kr_symm_barrier": (c_int, [_P, c_int, c_int, c_int, _P]),
     "kr_sync_test": (c_int, [_P, c_int, c_int, _P, _P, c_int, c_int, c_int, _P]),
     # host model of the barrier protocol

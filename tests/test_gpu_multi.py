@@ -1,4 +1,4 @@
-"""Multi-GPU tests (2 to 4 ranks, one process per GPU, NCCL for bootstrap and goldens): the native
+"""Multi-GPU tests (2, 4 and 8 ranks, one process per GPU, NCCL for bootstrap and goldens): the native
 symmetric allocator's rendezvous, every comm op, every fused op, and the timeout path when a rank
 skips a collective. Mirrors the reference's test matrix (test/test_allreduce.py, test_allgather.py,
 test_allgather_matmul.py, test_allreduce_bias.py, test_allreduce_bias_rms_norm.py,
@@ -127,16 +127,30 @@ def _all_ops(rank, ws):
                 torch.cuda.synchronize()
                 assert torch.equal(ag, a_full), (backend, splits)
                 torch.testing.assert_close(c.float(), gold_c, atol=1e-1, rtol=1e-1)
-    # -- GEMM + reduce-scatter, both variants (reference: test/test_gemm_reduce_scatter.py)
-    M, Kl, N2 = 256 * ws, 1024, 1024
-    a = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
-    bt2 = (0.05 * torch.randn(N2, Kl, device=dev)).to(torch.bfloat16)
-    full = nccl_sum(a.float() @ bt2.float().t())
-    ms = M // ws
-    for fn in (fused.gemm_reduce_scatter, fused.gemm_reduce_scatter_ce_persistent):
-        for _ in range(3):
-            r = fn(a, bt2.t())
-            torch.testing.assert_close(r.float(), full[rank * ms:(rank + 1) * ms], atol=1e-1, rtol=5e-2)
+    # -- GEMM + reduce-scatter: both exchange algorithms and the copy-engine variant
+    #    (reference: test/test_gemm_reduce_scatter.py); the second shape gives every CTA pair
+    #    several 256 x 256 tiles (the tensor-parallel MLP's M = 2048, N = 8192)
+    for M, Kl, N2 in ((256 * ws, 1024, 1024), (2048, 1024, 8192)):
+        a = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
+        bt2 = (0.05 * torch.randn(N2, Kl, device=dev)).to(torch.bfloat16)
+        full = nccl_sum(a.float() @ bt2.float().t())
+        ms = M // ws
+        gold_rs = full[rank * ms:(rank + 1) * ms]
+        variants = [lambda: fused.gemm_reduce_scatter(a, bt2.t(), algo="pull"),
+                    lambda: fused.gemm_reduce_scatter(a, bt2.t(), algo="push"),
+                    lambda: fused.gemm_reduce_scatter_ce_persistent(a, bt2.t())]
+        for fn in variants:
+            first = None
+            for _ in range(3):
+                r = fn()
+                torch.testing.assert_close(r.float(), gold_rs, atol=1e-1, rtol=5e-2)
+                if first is None:
+                    first = r.clone()
+                else:
+                    assert torch.equal(first, r)      # same bits from call to call
+        torch.cuda.synchronize()
+        kraken_b200.check_status()
+        dist.barrier()
     a_u = torch.randn(64 * ws, 256, device=dev).to(torch.bfloat16)          # slab not a multiple of 128
     bt_u = (0.05 * torch.randn(512, 256, device=dev)).to(torch.bfloat16)
     full_u = nccl_sum(a_u.float() @ bt_u.float().t())
@@ -201,9 +215,11 @@ def _rank_skips_collective(rank, ws):
     kraken_b200.check_status()
 
 
-@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
-def test_all_ops_multi_gpu():
-    run_distributed(_all_ops, min(_ngpu(), 4), "nccl")
+@pytest.mark.parametrize("ws", [2, 4, 8])
+def test_all_ops_multi_gpu(ws):
+    if _ngpu() < ws:
+        pytest.skip(f"needs {ws} GPUs")
+    run_distributed(_all_ops, ws, "nccl")
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
