@@ -136,11 +136,14 @@ struct RsPullHooks : HookDefaults {
 
   // Sums 128-row tile (tr, tc) over all ranks into `out`. Thread tid of 128 handles 16-byte
   // vectors tid, tid + 128, ...: a warp covers one 512-byte row segment per instruction.
-  __device__ __forceinline__ bool reduce_unit(const GemmParams& p, int tr, int tc, int tid) {
+  __device__ __forceinline__ bool reduce_unit(const GemmParams& p, int tr, int tc, int tid, int slot) {
     uint32_t* f = counter(p, p.rank, tr, tc);
     const uint32_t need = (uint32_t)p.ws;
-    if (tid == 0)
+    if (tid == 0) {
+      trace_put(p, 2, slot, 0);
       spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 57, 0, blockIdx.x));
+      trace_put(p, 2, slot, 1);
+    }
     reducer_bar_sync();
     if (!status_ok(p.sync)) return false;
     const int N = p.rows_c;
@@ -212,7 +215,10 @@ struct RsPullHooks : HookDefaults {
       }
     }
     // counter back to zero for the call after next (the next one uses the other bank)
-    if (tid == 0) red_add_relaxed_sys(f, 0u - need);
+    if (tid == 0) {
+      red_add_relaxed_sys(f, 0u - need);
+      trace_put(p, 2, slot, 2);
+    }
     return true;
   }
 
@@ -222,6 +228,7 @@ struct RsPullHooks : HookDefaults {
     const int total = p.tiles_r * p.tiles_c;
     const int rows_per_tile = half < 0 ? kBM : 2 * kBM;
     unsigned own = 0;
+    int served = 0;
     for (int t = 0; t < total; ++t) {
       int trv, tc;
       tile_coords(p, t, trv, tc);
@@ -231,7 +238,7 @@ struct RsPullHooks : HookDefaults {
       if (!mine) continue;
       const int tr = half < 0 ? trv : 2 * trv + half;
       if (tr * kBM >= p.rows_r) continue;
-      if (!reduce_unit(p, tr, tc, tid)) return;
+      if (!reduce_unit(p, tr, tc, tid, served++)) return;
     }
   }
 };
@@ -342,9 +349,20 @@ static int rs_plan(int M, int N, int ws, int rank, int algo, unsigned cap, bool 
   return KR_SUCCESS;
 }
 
+static unsigned long long* g_rs_trace = nullptr;
+static unsigned long long g_rs_trace_words = 0;
+
 }  // namespace kraken
 
 using namespace kraken;
+
+// Per-tile timeline of the next reduce-scatter GEMM launches on this process: `buf` is device memory
+// of `words` 64-bit words (at least CTAs * 3 * 64 * 4), or nullptr to switch the timeline off.
+KR_API int kr_gemm_rs_set_trace(unsigned long long* buf, unsigned long long words) {
+  g_rs_trace = buf;
+  g_rs_trace_words = words;
+  return KR_SUCCESS;
+}
 
 // out[0..7] = {pair, tiles_r, tiles_c, group_r, pivot_r, interleave_r, workers, grid} for the
 // given problem on a device with `num_ctas` CTAs available. For tests of the flag protocol.
@@ -427,6 +445,11 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
   p.pivot_r = pl.pivot_r;
   p.interleave_r = pl.interleave_r;
   p.num_mma_ctas = pl.grid;
+  if (g_rs_trace != nullptr && !emu_recorder().active) {
+    KR_REQUIRE(g_rs_trace_words >= (unsigned long long)pl.grid * kTraceRoles * kTraceTiles * kTraceFields,
+               "trace buffer too small for this launch");
+    p.trace = g_rs_trace;
+  }
   const unsigned threads = algo == 0 ? kGemmThreads : kRsPullThreads;
   if (pl.pair) {
     // each CTA of a pair loads its own 128 rows of the column operand: box of 128 rows, not 256

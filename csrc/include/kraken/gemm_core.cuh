@@ -89,6 +89,8 @@ struct alignas(64) GemmParams {
   int slab_rows;             // M / ws
   int rs_algo;               // 0: push partial tiles to the owner; 1: owner pulls and reduces (NVLS or peer loads)
   SyncCtx sync;
+  // optional per-tile timeline (nullptr: off): [CTA][role][tile slot][field] %globaltimer stamps
+  unsigned long long* trace;
   // host-side bookkeeping (not read on the device): the column operand as given, so that a
   // launcher can re-encode its tensor map with another box height
   const void* host_c_ptr;
@@ -111,6 +113,19 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int t,
   // Interleaved slabs: consecutive row tiles of the order belong to consecutive slabs (owners), so
   // every owner's tiles finish at an even rate instead of slab after slab.
   if (p.interleave_r > 1) tr = (tr % p.interleave_r) * (p.tiles_r / p.interleave_r) + tr / p.interleave_r;
+}
+
+// Per-tile timeline for performance work: when GemmParams::trace is set, one thread per role
+// stamps %globaltimer at fixed points of every tile it handles (first kTraceTiles tiles per CTA).
+//   role 0 (MMA issuer):  0 accumulator free, 1 first operand stage landed, 2 last MMA issued
+//   role 1 (epilogue):    0 accumulator complete, 1 tile stored (stores issued), 2 completion hook done
+//   role 2 (side role):   0 wait begins, 1 wait over, 2 work item done
+constexpr int kTraceTiles = 64;
+constexpr int kTraceRoles = 3;
+constexpr int kTraceFields = 4;
+__device__ __forceinline__ void trace_put(const GemmParams& p, int role, int slot, int field) {
+  if (p.trace != nullptr && slot < kTraceTiles)
+    p.trace[(((size_t)blockIdx.x * kTraceRoles + role) * kTraceTiles + slot) * kTraceFields + field] = globaltimer_ns();
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -396,11 +411,13 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, p.sync, 41);
         if (!ok) break;
         tc_fence_after();
+        trace_put(p, 0, it, 0);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(full_bar(s), ph, p.sync, 42);
           if (!ok) break;
           tc_fence_after();
+          if (kb == 0) trace_put(p, 0, it, 1);
           const uint32_t sa = stage0 + s * Cfg::STAGE;
           const uint64_t adesc = make_smem_desc_sw128(sa);
           const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
@@ -411,6 +428,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
           if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
         }
         if (ok) umma_commit(tfull_bar(acc));   // accumulator complete
+        trace_put(p, 0, it, 2);
       }
     }
   } else if (warp >= 6) {
@@ -433,6 +451,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 0);
       if (defer && prev_tr >= 0 && hooks.may_wait(p, tr)) {
         // never block on a peer while a finished tile's signal is still held back
         if (lane == 0) {
@@ -446,6 +465,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       }
       ok = gemm_epilogue_tile<BN, false>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, tempty_bar(acc), defer);
       if (!ok) break;
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 1);
       if (defer) {
         if (prev_tr >= 0) ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
         prev_tr = tr;
@@ -453,6 +473,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       } else {
         ok = hooks.after_store(p, tr, tc, q, lane);
       }
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 2);
     }
     if (defer && prev_tr >= 0) {
       if (lane == 0) {
@@ -588,11 +609,13 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, p.sync, 45);
         if (!ok) break;
         tc_fence_after();
+        trace_put(p, 0, it, 0);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * Cfg::BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(full_bar(s), ph, p.sync, 46);
           if (!ok) break;
           tc_fence_after();
+          if (kb == 0) trace_put(p, 0, it, 1);
           const uint32_t sa = stage0 + s * Cfg::STAGE;
           const uint64_t adesc = make_smem_desc_sw128(sa);
           const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
@@ -607,6 +630,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
           umma_commit_pair(tfull_bar(acc));
           umma_commit_pair(peer_tfull[acc]);
         }
+        trace_put(p, 0, it, 2);
       }
     }
   } else if (warp >= 6) {
@@ -630,6 +654,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 0);
       if (defer && prev_tr >= 0 && hooks.may_wait(p, tr)) {
         if (lane == 0) {
           bulk_wait_group<0>();
@@ -642,6 +667,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       }
       ok = gemm_epilogue_tile<Cfg::BN, true>(p, hooks, tr, tc, acc, tmem_base, q, lane, stg, lead_tempty[acc], defer);
       if (!ok) break;
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 1);
       if (defer) {
         if (prev_tr >= 0) ok = hooks.after_store(p, prev_tr, prev_tc, q, lane);
         prev_tr = tr;
@@ -649,6 +675,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       } else {
         ok = hooks.after_store(p, tr, tc, q, lane);
       }
+      if (q == 0 && lane == 0) trace_put(p, 1, it, 2);
     }
     if (defer && prev_tr >= 0) {
       if (lane == 0) {

@@ -8,12 +8,9 @@
 // kraken/fused/two_shot_all_reduce_bias_rms_norm.py:27-223.
 // y = x * rsqrt(mean(x^2) + eps) * w, fp32 math, bf16 in/out.
 #include "kraken/host.h"
-#include "kraken/vec.cuh"
+#include "kraken/norm_core.cuh"
 
 namespace kraken {
-
-constexpr int kNormMaxThreads = 1024;
-constexpr int kNormVpt = 4;   // 16-byte vectors a thread keeps in registers per row
 
 struct NormParams {
   void* const* bufs;       // [ws] symmetric buffers (AR variants)
@@ -33,43 +30,6 @@ struct NormParams {
 };
 
 __device__ __forceinline__ char* symm_buf(const NormParams& p, int r) { return (char*)p.bufs[r] + p.buf_off; }
-
-__device__ __forceinline__ float block_sum(float v, float* smem) {
-  v = warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
-  __syncthreads();   // smem reuse across rows
-  if (lane == 0) smem[warp] = v;
-  __syncthreads();
-  float t = (lane < nwarps) ? smem[lane] : 0.f;
-  return warp_sum(t);
-}
-
-// Normalises the row held in f[][] (vectors threadIdx.x + i*blockDim.x) and writes it to yrow.
-__device__ __forceinline__ void rms_finish(float (&f)[kNormVpt][8], int nvec, int D, float eps, const char* w,
-                                           char* yrow, float* smem) {
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < kNormVpt; ++i) {
-    int v = threadIdx.x + i * blockDim.x;
-    if (v < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += f[i][j] * f[i][j];
-    }
-  }
-  ss = block_sum(ss, smem);
-  const float inv = rsqrtf(ss / (float)D + eps);
-#pragma unroll
-  for (int i = 0; i < kNormVpt; ++i) {
-    int v = threadIdx.x + i * blockDim.x;
-    if (v < nvec) {
-      float g[8];
-      unpack8(ld16_nc(w + (size_t)v * 16), g);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) g[j] = f[i][j] * inv * g[j];
-      st16(yrow + (size_t)v * 16, pack8(g));
-    }
-  }
-}
 
 // ---- standalone RMSNorm ----------------------------------------------------------------------
 __global__ void __launch_bounds__(kNormMaxThreads) rms_norm_kernel(const __grid_constant__ NormParams p) {

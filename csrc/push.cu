@@ -1,0 +1,214 @@
+// Push-style one-shot all-reduce for small messages, optionally fused with a bias add and with
+// bias + RMSNorm (the tensor-parallel decode epilogue).
+//
+// The pull form (comm.cu / norm.cu; reference: kraken/comm/one_shot_all_reduce.py:17-54,
+// kraken/fused/one_shot_all_reduce_bias_rms_norm.py:23-99) costs a copy-in, a barrier, a round of
+// remote loads and an exit barrier. Here every rank WRITES its data straight into slot [rank] of
+// every peer's workspace (posted NVLink stores, or one multimem.st through the NVSwitch), meets its
+// peers in ONE barrier, and then sums the ws slots out of its own memory. The workspace has two
+// halves used alternately call by call, so a fast rank's next call never overwrites what a slow
+// rank still reads and no exit barrier is needed: a rank can only be one call ahead, because
+// finishing a call takes a signal from every peer sent in that same call.
+// The peers' buffer and signal-pad addresses travel in the kernel parameters (world sizes up to
+// 8), which saves two dependent global loads at the start of a latency-bound kernel.
+#include "kraken/host.h"
+#include "kraken/norm_core.cuh"
+
+namespace kraken {
+
+constexpr int kPushMaxWs = 8;
+constexpr int kPushThreads = 512;
+
+struct PushParams {
+  void* bufs[kPushMaxWs];        // every rank's workspace
+  uint32_t* pads[kPushMaxWs];    // every rank's signal pad
+  void* mc_ptr;                  // multicast address of the workspace, or nullptr
+  const void* input;             // this rank's data (any device memory)
+  void* output;
+  const void* bias;              // optional
+  const void* w;                 // RMSNorm weight (norm kernel)
+  unsigned long long numel;      // elements (all-reduce kernel)
+  unsigned long long bias_period;
+  unsigned long long half_off;   // byte offset of this call's workspace half
+  unsigned long long slot_bytes; // bytes reserved per source rank inside a half
+  int rows, D;                   // norm kernel
+  float eps;
+  int rank, ws;
+  uint32_t pad_base;
+  SyncCtx sync;
+};
+
+__device__ __forceinline__ char* slot_of(const PushParams& p, int dst, int src) {
+  return (char*)p.bufs[dst] + p.half_off + (size_t)src * p.slot_bytes;
+}
+
+// Writes one 16-byte vector of this rank's data into slot [rank] of every peer.
+__device__ __forceinline__ void push_vec(const PushParams& p, size_t byte_off, const U4& x) {
+  if (p.mc_ptr != nullptr) {
+    multimem_st16((char*)p.mc_ptr + p.half_off + (size_t)p.rank * p.slot_bytes + byte_off, x);
+  } else {
+#pragma unroll
+    for (int s = 1; s < kPushMaxWs; ++s)
+      if (s < p.ws) {
+        int peer = p.rank + s;
+        if (peer >= p.ws) peer -= p.ws;
+        st16(slot_of(p, peer, p.rank) + byte_off, x);
+      }
+  }
+}
+
+// Sum over ranks (rank order) of one vector: the own contribution is still in registers.
+__device__ __forceinline__ void gather_vec(const PushParams& p, size_t byte_off, const U4& own, float (&f)[8]) {
+  U4 x[kPushMaxWs];
+#pragma unroll
+  for (int s = 0; s < kPushMaxWs; ++s)
+    if (s < p.ws && s != p.rank) x[s] = ld16(slot_of(p, p.rank, s) + byte_off);
+#pragma unroll
+  for (int s = 0; s < kPushMaxWs; ++s)
+    if (s < p.ws) acc8(s == p.rank ? own : x[s], f);
+}
+
+// ---- all-reduce (+bias) ---------------------------------------------------------------------
+// Block b handles vectors b*T + t, (b + nb)*T + t, ... in both phases on every rank, so the
+// per-block barrier is all the ordering the slots need.
+__device__ void push_ar_body(const PushParams& p, unsigned bid, unsigned nb) {
+  const size_t nvec = p.numel / 8;
+  const size_t stride = (size_t)nb * blockDim.x;
+  const size_t first = (size_t)bid * blockDim.x + threadIdx.x;
+  for (size_t v = first; v < nvec; v += stride) push_vec(p, v * 16, ld16((const char*)p.input + v * 16));
+  if (!symm_mem_sync<true, true>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 60)) return;
+  for (size_t v = first; v < nvec; v += stride) {
+    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (p.bias) acc8(ld16_nc((const char*)p.bias + ((v * 8) % p.bias_period) * 2), f);
+    gather_vec(p, v * 16, ld16((const char*)p.input + v * 16), f);
+    st16((char*)p.output + v * 16, pack8(f));
+  }
+}
+KR_DEFINE_RANKED_KERNEL(push_ar, PushParams, kPushThreads)
+
+// ---- all-reduce + bias + RMSNorm --------------------------------------------------------------
+// One block per row (row r -> block r % nb on every rank); a thread keeps up to kNormVpt vectors
+// of the row in registers from the push to the normalisation.
+__device__ void push_ar_norm_body(const PushParams& p, unsigned bid, unsigned nb) {
+  __shared__ float smem[32];
+  const int nvec = p.D / 8;
+  // phase 1: all rows of this block go out before the barrier
+  for (int r = bid; r < p.rows; r += nb) {
+    const size_t off = (size_t)r * p.D * 2;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      const size_t bo = off + (size_t)v * 16;
+      push_vec(p, bo, ld16((const char*)p.input + bo));
+    }
+  }
+  if (!symm_mem_sync<true, true>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 61)) return;
+  for (int r = bid; r < p.rows; r += nb) {
+    const size_t off = (size_t)r * p.D * 2;
+    float f[kNormVpt][8];
+#pragma unroll
+    for (int i = 0; i < kNormVpt; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        const size_t bo = off + (size_t)v * 16;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[i][j] = 0.f;
+        if (p.bias) acc8(ld16_nc((const char*)p.bias + (((size_t)r * p.D + (size_t)v * 8) % p.bias_period) * 2), f[i]);
+        gather_vec(p, bo, ld16((const char*)p.input + bo), f[i]);
+      }
+    }
+    rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.output + off, smem);
+  }
+}
+KR_DEFINE_RANKED_KERNEL(push_ar_norm, PushParams, kNormMaxThreads)
+
+}  // namespace kraken
+
+using namespace kraken;
+
+static int fill_push(PushParams& p, DeviceState* d, void* const* bufs_host, uint32_t* const* pads_host, void* mc_ptr,
+                     int rank, int ws, const void* input, void* output, const void* bias,
+                     unsigned long long bias_numel, unsigned long long bytes, int call_parity,
+                     unsigned long long workspace_bytes, uint32_t pad_base) {
+  KR_REQUIRE(ws >= 1 && ws <= kPushMaxWs && rank >= 0 && rank < ws, "push all-reduce supports world sizes up to 8");
+  KR_REQUIRE(bufs_host != nullptr && pads_host != nullptr, "null argument");
+  KR_REQUIRE(pad_base % ws == 0, "pad_base must be a multiple of the world size");
+  KR_REQUIRE((((uintptr_t)input | (uintptr_t)output | (uintptr_t)bias) & 15) == 0, "tensors must be 16-byte aligned");
+  if (bias) KR_REQUIRE(bias_numel > 0 && bias_numel % 8 == 0, "bias length must be a positive multiple of 8");
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < ws; ++r) {
+    p.bufs[r] = bufs_host[r];
+    p.pads[r] = pads_host[r];
+  }
+  const unsigned long long half = workspace_bytes / 2 / 1024 * 1024;
+  const unsigned long long slot = half / ws / 1024 * 1024;
+  KR_REQUIRE(slot >= bytes && slot > 0, "push workspace too small for this message");
+  p.mc_ptr = mc_ptr;
+  p.input = input;
+  p.output = output;
+  p.bias = bias;
+  p.bias_period = bias ? bias_numel : 8;
+  p.half_off = (call_parity & 1) ? half : 0;
+  p.slot_bytes = slot;
+  p.rank = rank;
+  p.ws = ws;
+  p.pad_base = pad_base;
+  p.sync = sync_ctx(d);
+  return KR_SUCCESS;
+}
+
+static unsigned push_grid_cap(const DeviceState* d) {
+  unsigned cap = (unsigned)d->num_sms;
+  if (emu_recorder().active) {
+    cap /= (unsigned)emu_recorder().ws;
+    if (cap < 1) cap = 1;
+  }
+  return cap;
+}
+
+// output = bias + sum_r input_r. bufs_host / pads_host: HOST arrays [ws] with every rank's
+// workspace and signal-pad address; workspace_bytes per rank, two halves alternating with
+// call_parity, each cut into ws slots that must hold numel * 2 bytes. numel % 8 == 0.
+KR_API int kr_push_all_reduce(void* const* bufs_host, uint32_t* const* pads_host, void* mc_ptr, int rank, int ws,
+                              const void* input, void* output, const void* bias, unsigned long long bias_numel,
+                              unsigned long long numel, int call_parity, unsigned long long workspace_bytes,
+                              uint32_t pad_base, cudaStream_t stream) {
+  DeviceState* d = device_state();
+  if (!d) return KR_FAIL_CUDA;
+  KR_REQUIRE(numel >= 8 && numel % 8 == 0, "push all-reduce needs numel % 8 == 0");
+  PushParams p;
+  int rc = fill_push(p, d, bufs_host, pads_host, mc_ptr, rank, ws, input, output, bias, bias_numel, numel * 2,
+                     call_parity, workspace_bytes, pad_base);
+  if (rc) return rc;
+  p.numel = numel;
+  const unsigned long long nvec = numel / 8;
+  unsigned nb = cdiv(nvec, (size_t)kPushThreads * 2);
+  if (nvec <= (unsigned long long)kPushThreads) nb = 1;
+  if (nb > push_grid_cap(d)) nb = push_grid_cap(d);
+  return launch_ranked(push_ar_kernel, push_ar_emu_kernel, p, nb, kPushThreads, 0, stream);
+}
+
+// y = rms_norm(bias + sum_r x_r) * w over rows of D elements (D % 8 == 0, D / 8 <= 4096).
+KR_API int kr_push_all_reduce_bias_rms_norm(void* const* bufs_host, uint32_t* const* pads_host, void* mc_ptr, int rank,
+                                            int ws, const void* x, const void* bias, unsigned long long bias_numel,
+                                            const void* w, void* y, int rows, int D, float eps, int call_parity,
+                                            unsigned long long workspace_bytes, uint32_t pad_base,
+                                            cudaStream_t stream) {
+  DeviceState* d = device_state();
+  if (!d) return KR_FAIL_CUDA;
+  KR_REQUIRE(rows >= 1 && D > 0 && D % 8 == 0, "needs D % 8 == 0");
+  KR_REQUIRE(D / 8 <= kNormVpt * kNormMaxThreads, "row too long for the fused all-reduce + RMSNorm kernel");
+  KR_REQUIRE(((uintptr_t)w & 15) == 0, "tensors must be 16-byte aligned");
+  PushParams p;
+  int rc = fill_push(p, d, bufs_host, pads_host, mc_ptr, rank, ws, x, y, bias, bias_numel,
+                     (unsigned long long)rows * D * 2, call_parity, workspace_bytes, pad_base);
+  if (rc) return rc;
+  p.w = w;
+  p.rows = rows;
+  p.D = D;
+  p.eps = eps;
+  const unsigned cap = push_grid_cap(d);
+  const unsigned nb = (unsigned)rows < cap ? (unsigned)rows : cap;
+  unsigned nt = ((unsigned)D / 8 + 31) / 32 * 32;      // one vector per thread when the row allows
+  if (nt < 64) nt = 64;
+  if (nt > kNormMaxThreads) nt = kNormMaxThreads;
+  return launch_ranked(push_ar_norm_kernel, push_ar_norm_emu_kernel, p, nb, nt, 0, stream);
+}

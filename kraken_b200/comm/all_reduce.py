@@ -13,13 +13,51 @@ import torch
 
 from .. import _reference as ref
 from .. import config
+from .._logging import utils as _log
 from ..ops import lib as _lib
 from ..parallel import symm_mem
 
 
-def _dump(msg: str, hdl) -> None:
-    if config.dump_kernel() and hdl.rank == 0:
-        print(f"[kraken_b200] {msg}", flush=True)
+def _dump(msg: str, hdl=None) -> None:
+    op, _, detail = msg.partition(" ")
+    _log.log_kernel_choice(op, detail)
+
+
+# ---- push-style one-shot (small messages) ---------------------------------------------------------
+_PUSH_WORKSPACE_BYTES = 8 << 20      # two halves of world_size slots
+
+
+def push_limit_bytes(ws: int) -> int:
+    """Largest message the push-style one-shot kernels take: (ws - 1) x S leaves each rank, so the
+    limit shrinks with the world size (512 KiB at 8 ranks, 2 MiB at 2)."""
+    return (_PUSH_WORKSPACE_BYTES // 2 // max(1, ws)) // 1024 * 1024
+
+
+def push_eligible(nbytes: int, numel: int, ws: int, kwargs=None) -> bool:
+    mode = (kwargs or {}).get("algo") or config.one_shot_mode()
+    return mode == "push" and 1 <= ws <= 8 and numel % 8 == 0 and 16 <= nbytes <= push_limit_bytes(ws)
+
+
+def push_workspace(group, device):
+    """(handle, host array of signal-pad addresses, parity of this call) of the push workspace."""
+    import ctypes
+
+    hdl = symm_mem.get_symm_mem_workspace(group, _PUSH_WORKSPACE_BYTES, device, kind="push")
+    pads = getattr(hdl, "_host_pad_array", None)
+    if pads is None:
+        pads = hdl._host_pad_array = (ctypes.c_void_p * hdl.world_size)(*hdl.signal_pad_ptrs)
+    calls = getattr(hdl, "_push_calls", 0)
+    hdl._push_calls = calls + 1
+    return hdl, pads, calls & 1
+
+
+def _push_all_reduce(inp: torch.Tensor, bias, out: torch.Tensor, group) -> None:
+    hdl, pads, parity = push_workspace(group, inp.device)
+    bias_ptr, bias_n = _bias_args(bias, inp)
+    _dump(f"one_shot_all_reduce push numel={inp.numel()} ws={hdl.world_size} nvls={bool(hdl.multicast_ptr)}")
+    _lib.check(_lib.lib().kr_push_all_reduce(
+        hdl._host_ptr_array, pads, hdl.multicast_ptr or None, hdl.rank, hdl.world_size, inp.data_ptr(), out.data_ptr(),
+        bias_ptr, bias_n, inp.numel(), parity, hdl.buffer_size, 0, _lib.current_stream_ptr()))
 
 
 def _check_bf16(t: torch.Tensor) -> None:
@@ -49,13 +87,19 @@ def _max_blocks(kwargs) -> int:
 
 def one_shot_all_reduce(tensor: torch.Tensor, **kwargs) -> torch.Tensor:
     """output = sum over ranks of `tensor`. `tensor` must live in symmetric memory
-    (``symm_mem.empty``); every rank reads all peers' copies directly. fp32 accumulation."""
+    (``symm_mem.empty``). Small messages are pushed: every rank writes its data into a slot of each
+    peer's workspace, one barrier, local sum. Larger ones are pulled: every rank reads all peers'
+    copies directly. fp32 accumulation in rank order. kwargs: group, max_num_blocks,
+    algo="push"|"pull" (default KRAKEN_ONE_SHOT)."""
     if tensor.device.type != "cuda":
         return ref.all_reduce(tensor, kwargs.get("group"))
     _check_bf16(tensor)
     hdl = symm_mem.rendezvous(tensor, kwargs.get("group"))
     out = torch.empty_like(tensor)
-    _dump(f"one_shot_all_reduce numel={tensor.numel()} ws={hdl.world_size}", hdl)
+    if push_eligible(tensor.numel() * 2, tensor.numel(), hdl.world_size, kwargs):
+        _push_all_reduce(tensor, None, out, kwargs.get("group"))
+        return out
+    _dump(f"one_shot_all_reduce pull numel={tensor.numel()} ws={hdl.world_size}", hdl)
     _lib.check(_lib.lib().kr_one_shot_all_reduce(
         hdl.buffer_ptrs_dev, hdl.offset_of(tensor), hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, None,
         out.data_ptr(), None, 0, tensor.numel(), _max_blocks(kwargs), 0, _lib.current_stream_ptr()))

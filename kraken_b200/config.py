@@ -15,6 +15,8 @@ kraken/comm/two_shot_all_reduce.py:153).
                             inside the GEMM kernel pull the shards)
 ``KRAKEN_RS_ALGO``          ``pull`` (default: owners sum the ranks' staged tiles, in the NVSwitch when possible) or
                             ``push`` (partial tiles are pushed to the owner and summed in its epilogue)
+``KRAKEN_ONE_SHOT``         ``push`` (default: small one-shot all-reduces write into the peers' workspace and meet in
+                            one barrier) or ``pull`` (copy-in, barrier, remote loads, exit barrier)
 ``KRAKEN_NVTX``             ``1`` wraps every public op in an NVTX range named after it (for timeline tools)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
@@ -66,6 +68,11 @@ def ag_mode() -> str:
 def rs_algo() -> str:
     v = os.environ.get("KRAKEN_RS_ALGO", "pull").strip().lower()
     return v if v in ("pull", "push") else "pull"
+
+
+def one_shot_mode() -> str:
+    v = os.environ.get("KRAKEN_ONE_SHOT", "push").strip().lower()
+    return v if v in ("push", "pull") else "push"
 
 
 def dump_kernel() -> bool:

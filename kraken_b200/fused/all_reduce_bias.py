@@ -15,7 +15,7 @@ import torch
 
 from .. import _reference as ref
 from .. import config
-from ..comm.all_reduce import _bias_args, _check_bf16
+from ..comm.all_reduce import _bias_args, _check_bf16, _dump, _push_all_reduce, push_eligible, push_workspace
 from ..ops import lib as _lib
 from ..parallel import symm_mem
 
@@ -29,15 +29,21 @@ def _scratch(symm_buf: torch.Tensor, x: torch.Tensor, group):
 
 def one_shot_all_reduce_bias(symm_mem_buffer: torch.Tensor, input_tensor: torch.Tensor, bias: torch.Tensor | None,
                              output: torch.Tensor, max_num_blocks: int = 0, BLOCK_SIZE: int = 4096,
-                             group=None) -> None:
-    """output = all_reduce(input) (+ bias): every rank pulls all peers' copies and sums."""
+                             group=None, algo: str | None = None) -> None:
+    """output = all_reduce(input) (+ bias). Small messages: every rank writes its data into the
+    peers' workspace, one barrier, local sum (`symm_mem_buffer` is then not touched). Larger ones:
+    copy into `symm_mem_buffer`, barrier, every rank pulls all peers' copies and sums."""
     if input_tensor.device.type != "cuda":
         output.copy_(ref.all_reduce_bias(input_tensor, bias, group))
         return None
     _check_bf16(input_tensor)
     _check_bf16(output)
     hdl, off = _scratch(symm_mem_buffer, input_tensor, group)
+    if push_eligible(input_tensor.numel() * 2, input_tensor.numel(), hdl.world_size, {"algo": algo}):
+        _push_all_reduce(input_tensor, bias, output, group)
+        return None
     bias_ptr, bias_n = _bias_args(bias, input_tensor)
+    _dump(f"one_shot_all_reduce_bias pull numel={input_tensor.numel()} ws={hdl.world_size}")
     _lib.check(_lib.lib().kr_one_shot_all_reduce(
         hdl.buffer_ptrs_dev, off, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, input_tensor.data_ptr(),
         output.data_ptr(), bias_ptr, bias_n, input_tensor.numel(), int(max_num_blocks or 0), 0,
@@ -60,6 +66,7 @@ def two_shot_all_reduce_bias(symm_mem_input: torch.Tensor, input_tensor: torch.T
     hdl, off = _scratch(symm_mem_input, input_tensor, group)
     bias_ptr, bias_n = _bias_args(bias, input_tensor)
     mc = hdl.multicast_ptr if (hdl.multicast_ptr and config.force_algo() != "two_shot") else None
+    _dump(f"two_shot_all_reduce_bias numel={input_tensor.numel()} ws={hdl.world_size} nvls={bool(mc)}")
     _lib.check(_lib.lib().kr_two_shot_all_reduce(
         hdl.buffer_ptrs_dev, off, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, input_tensor.data_ptr(),
         output.data_ptr(), bias_ptr, bias_n, input_tensor.numel(), mc, int(max_num_blocks or 0), 0,
@@ -67,7 +74,7 @@ def two_shot_all_reduce_bias(symm_mem_input: torch.Tensor, input_tensor: torch.T
     return output
 
 
-def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int) -> None:
+def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int, one_shot: str | None = None) -> None:
     if x.device.type != "cuda":
         y.copy_(ref.all_reduce_bias_rms_norm(x, bias, w, eps, group))
         return
@@ -79,9 +86,17 @@ def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int) -> None:
         raise ValueError("RMSNorm weight must have the last dimension's size")
     hdl, off = _scratch(symm_buf, x, group)
     bias_ptr, bias_n = _bias_args(bias, x)
+    if algo == 0 and push_eligible(x.numel() * 2, x.numel(), hdl.world_size, {"algo": one_shot}):
+        ph, pads, parity = push_workspace(group, x.device)
+        _dump(f"one_shot_all_reduce_bias_rms_norm push rows={rows} D={D} ws={ph.world_size} nvls={bool(ph.multicast_ptr)}")
+        _lib.check(_lib.lib().kr_push_all_reduce_bias_rms_norm(
+            ph._host_ptr_array, pads, ph.multicast_ptr or None, ph.rank, ph.world_size, x.data_ptr(), bias_ptr, bias_n,
+            w.data_ptr(), y.data_ptr(), rows, D, float(eps), parity, ph.buffer_size, 0, _lib.current_stream_ptr()))
+        return
     mc = None
     if algo == 1 and hdl.multicast_ptr and config.force_algo() != "two_shot":
         algo, mc = 2, hdl.multicast_ptr
+    _dump(f"all_reduce_bias_rms_norm {('one_shot pull', 'two_shot', 'two_shot nvls')[algo]} rows={rows} D={D} ws={hdl.world_size}")
     _lib.check(_lib.lib().kr_all_reduce_bias_rms_norm(
         hdl.buffer_ptrs_dev, off, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, x.data_ptr(), bias_ptr, bias_n,
         w.data_ptr(), y.data_ptr(), rows, D, float(eps), algo, mc, 0, _lib.current_stream_ptr()))
@@ -89,9 +104,10 @@ def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int) -> None:
 
 def one_shot_all_reduce_bias_rms_norm(symm_mem_input: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None,
                                       w: torch.Tensor, y: torch.Tensor, eps: float = 1e-5, BLOCK_SIZE: int = 1024,
-                                      group=None) -> None:
-    """y = rms_norm(all_reduce(x) + bias) * w; the summed row never leaves registers."""
-    _ar_bias_rms_norm(symm_mem_input, x, bias, w, y, eps, group, 0)
+                                      group=None, algo: str | None = None) -> None:
+    """y = rms_norm(all_reduce(x) + bias) * w; the summed row never leaves registers. Small inputs
+    take the push form (one barrier), larger ones the pull form; algo="push"|"pull" overrides."""
+    _ar_bias_rms_norm(symm_mem_input, x, bias, w, y, eps, group, 0, algo)
 
 
 def two_shot_all_reduce_bias_rms_norm(symm_mem_input: torch.Tensor, x: torch.Tensor, bias: torch.Tensor | None,

@@ -160,3 +160,48 @@ def test_all_reduce_bias_rms_norm(ws, b, D):
             world.run(lambda r: fn(pads[r], xs[r], bb, w, ys[r], 1e-5))
             for r in range(ws):
                 torch.testing.assert_close(ys[r].float(), expect, atol=4e-2, rtol=4e-2)
+
+
+# ---- push-style one-shot kernels (small messages) ------------------------------------------------
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+@pytest.mark.parametrize("numel", [8, 2048, 5120 * 3, 64 * 1024])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_push_and_pull_one_shot_agree(ws, numel, with_bias):
+    world = EmuWorld(ws)
+    xs = _inputs(ws, (numel,), seed=31)
+    bias = torch.randn(numel, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda() if with_bias else None
+    expect = sum(x.float() for x in xs) + (bias.float() if with_bias else 0.0)
+    pads = world.symmetric((numel,), torch.bfloat16)
+    res = {}
+    for algo in ("push", "pull"):
+        for _ in range(3):          # three calls: both workspace halves, then the first again
+            outs = [torch.empty_like(xs[r]) for r in range(ws)]
+            for o in outs:
+                _poison(o)
+            world.run(lambda r: fused.one_shot_all_reduce_bias(pads[r], xs[r], bias, outs[r], algo=algo))
+            for r in range(ws):
+                torch.testing.assert_close(outs[r].float(), expect, atol=5e-2, rtol=5e-2)
+        res[algo] = outs
+    for r in range(ws):
+        assert torch.equal(res["push"][0], res["push"][r])      # rank-order sums: same bits on every rank
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+@pytest.mark.parametrize("b,D", [(1, 5120), (3, 5120), (16, 1024), (40, 8192), (2, 64)])
+def test_push_all_reduce_bias_rms_norm(ws, b, D):
+    world = EmuWorld(ws)
+    xs = _inputs(ws, (b, D), seed=33)
+    g = torch.Generator().manual_seed(6)
+    bias = torch.randn(D, generator=g).to(torch.bfloat16).cuda()
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).cuda()
+    s = sum(x.float() for x in xs) + bias.float()
+    expect = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    pads = world.symmetric((b, D), torch.bfloat16)
+    for algo in ("push", "pull"):
+        for _ in range(2):
+            ys = [torch.empty_like(xs[r]) for r in range(ws)]
+            for y in ys:
+                _poison(y)
+            world.run(lambda r: fused.one_shot_all_reduce_bias_rms_norm(pads[r], xs[r], bias, w, ys[r], 1e-5, algo=algo))
+            for r in range(ws):
+                torch.testing.assert_close(ys[r].float(), expect, atol=4e-2, rtol=4e-2)
