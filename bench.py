@@ -81,8 +81,6 @@ def run_ours(args):
         xb.copy_(x_host)
         x_bufs.append(xb)
     x_symm = x_bufs[0]
-    a_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
-    progress = torch.zeros(ws, dtype=torch.uint32, device=dev)
     result_host = torch.empty(1, dtype=torch.float32).pin_memory()
     copy_stream = torch.cuda.Stream()
 
@@ -92,7 +90,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     def step(x=None):
-        _, h = fused.all_gather_matmul(x_symm if x is None else x, w_up_t.t(), a_out=a_out, progress=progress)
+        _, h = fused.all_gather_matmul(x_symm if x is None else x, w_up_t.t())
         return fused.gemm_reduce_scatter(h, w_down_t.t())
 
     def run_e2e(k):
@@ -127,7 +125,7 @@ def run_ours(args):
         return t_begin.elapsed_time(t_end) / k
 
     def op_ag():
-        fused.all_gather_matmul(x_symm, w_up_t.t(), a_out=a_out, progress=progress)
+        fused.all_gather_matmul(x_symm, w_up_t.t())
 
     h_fixed = (torch.randn(M, Fl, generator=g).to(torch.bfloat16)).to(dev)
 

@@ -41,6 +41,8 @@ def main():
         golden = cublas_nccl().float()
         backends = {
             "kraken_b200": lambda: fused.gemm_reduce_scatter(a, b),
+            "kraken_b200_pull": lambda: fused.gemm_reduce_scatter(a, b, algo="pull"),
+            "kraken_b200_scatter": lambda: fused.gemm_reduce_scatter(a, b, algo="scatter"),
             "kraken_b200_push": lambda: fused.gemm_reduce_scatter(a, b, algo="push"),
             "kraken_b200_ce": lambda: fused.gemm_reduce_scatter_ce_persistent(a, b),
             "cublas_nccl": cublas_nccl,

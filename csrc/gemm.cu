@@ -51,9 +51,13 @@ struct AgHooks : HookDefaults {
       return true;
     }
     const int c_lo = lo / p.chunk_rows, c_hi = hi / p.chunk_rows;
-    for (int c = c_lo; c <= c_hi; ++c)
-      if (!wait_flag_acquire_gpu(p.progress + c, 1u, p.sync, 50)) return false;
-    fence_proxy_async();   // chunk was written through another proxy / by other CTAs
+    for (int c = c_lo; c <= c_hi; ++c) {
+      // push: the chunk's owner raises a flag in this rank's signal pad; else a local engine sets progress
+      const bool ok = p.ag_push ? wait_flag_acquire_sys(p.pads[p.rank] + p.flag_base + c, 1u, p.sync, 50)
+                                : wait_flag_acquire_gpu(p.progress + c, 1u, p.sync, 50);
+      if (!ok) return false;
+    }
+    fence_proxy_async();   // chunk was written through another proxy / by other CTAs or another GPU
     return true;
   }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
@@ -344,6 +348,107 @@ __device__ __forceinline__ void ag_comm_cta(const GemmParams& p, unsigned comm_i
 }
 
 // ---------------------------------------------------------------------------------------------
+// AG push engine: every rank writes its OWN shard into every peer's gathered buffer (local bulk
+// load -> shared memory -> bulk store to the peer: posted NVLink writes, no remote round trip) and
+// then raises the chunk's flag in that peer's signal pad. Destinations are served in the order
+// rank-1, rank-2, ...: a destination computes on the shards of rank+1, rank+2, ... in that order,
+// so each shard travels at full link rate exactly when it is needed next. The own copy goes last.
+// Flags live in two banks used alternately call by call and are put back to zero by the last CTA
+// of the launch; with the library's double-buffered gathered buffer no barrier is needed at all.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ag_push_cta(const GemmParams& p, unsigned comm_id, unsigned n_comm,
+                                            unsigned char* smem_raw) {
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + kAgSlots * kAgPiece;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAgSlots; ++s) mbar_init(bars + 8u * s, 1);
+    mbar_fence_init();
+  }
+  // A caller-owned gathered buffer may still be read by a slower peer's previous consumer.
+  if (p.ag_entry_barrier && !symm_mem_sync<true, true>(p.pads, p.pad_base / p.ws + comm_id, p.rank, p.ws, p.sync, 52)) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const size_t row_bytes = (size_t)p.K * 2;
+    const size_t chunk_bytes = (size_t)p.chunk_rows * row_bytes;
+    const size_t pieces = (chunk_bytes + kAgPiece - 1) / kAgPiece;
+    const char* shard = (const char*)p.ag_shard;
+    uint32_t issued = 0, stored = 0;   // piece counters over the ring
+    bool ok = true;
+    for (int step = 0; step < p.ws && ok; ++step) {
+      int dst = p.rank - 1 - step;
+      while (dst < 0) dst += p.ws;                       // ..., rank itself last
+      for (int sp = 0; sp < p.splits && ok; ++sp) {
+        const int idx = p.rank * p.splits + sp;
+        const char* from = shard + (size_t)sp * chunk_bytes;
+        char* to = (char*)p.bufs[dst] + p.ag_out_off + (size_t)idx * chunk_bytes;
+        size_t next_load = comm_id, next_store = comm_id;
+        while (next_store < pieces && ok) {
+          while (next_load < pieces && issued - stored < (uint32_t)(kAgSlots - 2)) {
+            const uint32_t slot = issued % kAgSlots;
+            if (issued >= (uint32_t)kAgSlots) bulk_wait_group_read<2>();
+            const size_t off = next_load * kAgPiece;
+            const uint32_t bytes = (uint32_t)min((size_t)kAgPiece, chunk_bytes - off);
+            mbar_expect_tx(bars + 8u * slot, bytes);
+            bulk_load_1d(base + slot * kAgPiece, from + off, bytes, bars + 8u * slot);
+            ++issued;
+            next_load += n_comm;
+          }
+          const uint32_t slot = stored % kAgSlots;
+          ok = mbar_wait(bars + 8u * slot, (stored / kAgSlots) & 1u, p.sync, 53);
+          if (!ok) break;
+          const size_t off = next_store * kAgPiece;
+          const uint32_t bytes = (uint32_t)min((size_t)kAgPiece, chunk_bytes - off);
+          fence_proxy_async();
+          bulk_store_1d(to + off, base + slot * kAgPiece, bytes);
+          bulk_commit_group();
+          ++stored;
+          next_store += n_comm;
+        }
+        if (!ok) break;
+        // my pieces of this chunk are at the destination before I count myself in; the comm CTA
+        // that completes the chunk tells the destination
+        bulk_wait_group<0>();
+        fence_proxy_async();
+        uint32_t* cnt = p.counters + (size_t)dst * p.splits + sp;
+        const uint32_t old = atom_add_acqrel_gpu(cnt, 1u);
+        if (old == n_comm - 1) {
+          *cnt = 0;
+          red_add_release_sys(p.pads[dst] + p.flag_base + idx, 1u);
+        }
+      }
+    }
+    bulk_wait_group<0>();
+    // the caller's progress words: in the order the chunks arrive here
+    if (comm_id == 0 && p.progress != nullptr) {
+      for (int step = 1; step <= p.ws && ok; ++step) {
+        const int src = (p.rank + step) % p.ws;
+        for (int sp = 0; sp < p.splits && ok; ++sp) {
+          const int idx = src * p.splits + sp;
+          ok = wait_flag_acquire_sys(p.pads[p.rank] + p.flag_base + idx, 1u, p.sync, 54);
+          if (ok) st_release_gpu(p.progress + idx, 1u);
+        }
+      }
+    }
+  }
+}
+
+// Push mode, every CTA on its way out: the last one puts this call's flag bank back to zero (all
+// peers have signalled — every consumer has seen every flag — and the peers' next signals to this
+// bank belong to the call after next).
+__device__ __forceinline__ void ag_push_finish(const GemmParams& p, unsigned num_ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* done = p.counters + (size_t)p.ws * p.splits;
+    const uint32_t old = atom_add_acqrel_gpu(done, 1u);
+    if (old == num_ctas - 1) {
+      *done = 0;
+      if (status_ok(p.sync))
+        for (int i = 0; i < p.ws * p.splits; ++i) st_relaxed_sys(p.pads[p.rank] + p.flag_base + i, 0u);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // kernels
 // ---------------------------------------------------------------------------------------------
 template <int BN>
@@ -356,12 +461,14 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
-      ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      else ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
       AgHooks h;
-    h.bn = BN;
+      h.bn = BN;
       gemm_mainloop<BN>(p, bid, n_mma, h, smem_raw);
     }
+    if (p.ag_push) ag_push_finish(p, nb);
   } else if (p.mode == GEMM_CE) {
     CeHooks h;
     h.bn = BN;
@@ -383,12 +490,14 @@ __device__ __forceinline__ void gemm_pair_body(const GemmParams& p, unsigned bid
     gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
-      ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      else ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
       AgHooks h;
-    h.bn = 256;
+      h.bn = 256;
       gemm_mainloop_pair(p, bid / 2, n_mma / 2, h, smem_raw);
     }
+    if (p.ag_push) ag_push_finish(p, nb);
   } else {
     CeHooks h;
     h.bn = 256;
@@ -646,13 +755,21 @@ KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long 
   return launch_gemm(bn, p, nb, stream);
 }
 
-// Fused all-gather -> GEMM. bufs[r] = rank r's A shard [shard_rows, K] (symmetric memory);
-// a_out [ws*shard_rows, K] receives the gathered A; c[ws*shard_rows, N] = a_out * bt^T.
-// progress [ws*splits] must be zero on entry; counters [ws*splits] zero (self-resetting).
+// Fused all-gather -> GEMM. a_out [ws*shard_rows, K] receives the gathered A; c[ws*shard_rows, N] =
+// a_out * bt^T. progress [ws*splits] must be zero on entry; counters [ws*splits + 1] zero
+// (self-resetting). Engines that fill a_out:
+//   push == 0: bufs[r] = rank r's A shard (symmetric memory); num_comm_ctas > 0 comm CTAs pull the
+//              shards, num_comm_ctas < 0: an external engine (copy engines) fills a_out and progress.
+//   push == 1: bufs[r] = the symmetric buffer that holds rank r's gathered A at byte offset a_out_off
+//              (a_out is this rank's address of it); num_comm_ctas comm CTAs push own_shard into every
+//              rank's buffer and raise flags in the signal pads from word flag_base on (zero on entry,
+//              zero again after the call; the caller alternates two banks). entry_barrier: wait for
+//              all ranks before the first remote write (needed unless the caller alternates buffers).
 KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void* own_shard, int rank, int ws,
                            void* a_out, const void* bt, long long ldb, void* c, long long ldc, int shard_rows, int N,
                            int K, int splits, uint32_t* progress, uint32_t* counters, int num_comm_ctas,
-                           uint32_t pad_base, cudaStream_t stream) {
+                           uint32_t pad_base, int push, unsigned long long a_out_off, uint32_t flag_base,
+                           unsigned long long pad_words, int entry_barrier, cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
@@ -685,6 +802,17 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   p.splits = splits;
   p.shard_rows = shard_rows;
   p.chunk_rows = shard_rows / splits;
+  p.ag_push = push ? 1 : 0;
+  p.ag_shard = own_shard;
+  p.ag_out_off = a_out_off;
+  p.ag_entry_barrier = entry_barrier ? 1 : 0;
+  if (push) {
+    KR_REQUIRE(num_comm_ctas > 0, "the push engine needs comm CTAs");
+    KR_REQUIRE((unsigned long long)flag_base + (unsigned long long)ws * splits <= pad_words, "signal pad too small for the chunk flags");
+    KR_REQUIRE(!entry_barrier || (unsigned long long)pad_base + (unsigned long long)d->num_sms * ws <= flag_base,
+               "barrier slots overlap chunk flags");
+    p.flag_base = flag_base;
+  }
   p.pivot_r = (rank * shard_rows) / kBM;   // start on (or next to) the local shard
   if (p.tiles_r > 0) p.pivot_r %= p.tiles_r;
   // group must not mix chunks of different arrival times more than necessary

@@ -3,15 +3,20 @@
 // C[M, N] = A[M, K_local] * Bt[N, K_local]^T is a partial sum on every rank; rank r ends up with
 // rows [r*M/ws, (r+1)*M/ws) of the sum over ranks. Two exchange algorithms share the main loop:
 //
-//  * pull (default): every rank TMA-stores ALL its partial tiles into its OWN symmetric staging
-//    matrix [M][N] (local traffic only, the epilogue never touches NVLink) and bumps a per-tile
-//    arrival counter in the tile owner's signal pad. Four extra "reducer" warps per CTA serve the
-//    tiles this rank owns: wait until all ws ranks have stored a tile, then sum it across ranks —
-//    in the NVSwitch with multimem.ld_reduce when the staging buffer has a multicast mapping,
-//    else with ws peer loads in rank order — and write the final rows. All ranks walk the tiles in
-//    the same order with the owners interleaved, so every owner's tiles complete at an even rate
-//    and the reduction of one tile overlaps the MMAs of the following ones. Staging halves and
-//    counter banks alternate call by call, so there is no grid-wide or cross-rank barrier at all.
+//  * pull: every rank TMA-stores ALL its partial tiles into its OWN symmetric staging matrix
+//    [M][N] (local traffic only, the epilogue never touches NVLink) and bumps a per-tile arrival
+//    counter in the tile owner's signal pad. Four extra "reducer" warps per CTA serve the tiles this
+//    rank owns, in work items of 16 rows dealt round-robin to all CTAs: wait until all ws ranks have
+//    stored the tile, then sum it across ranks with ws peer loads in rank order (or in the NVSwitch
+//    with multimem.ld_reduce when asked to) and write the final rows.
+//  * scatter: as pull, but the epilogue TMA-stores each tile into slot [rank] of the OWNER's
+//    staging [ws][M/ws][N] over NVLink (posted writes), so the reducer warps sum ws slots out of
+//    local memory.
+//    In both, all ranks walk the tiles in the same order with the owners interleaved, so every
+//    owner's tiles complete at an even rate and the reduction of one tile overlaps the MMAs of the
+//    following ones. Staging halves and counter banks alternate call by call (a rank can only be
+//    one call ahead of a peer: finishing a call takes a signal from every peer sent in that same
+//    call), so there is no grid-wide or cross-rank barrier at all.
 //  * push: the epilogue TMA-stores each remote tile into the owner's staging slab [src][M/ws][N]
 //    over NVLink and bumps the owner's counter; own-slab tiles are computed last, their epilogue
 //    waits for the ws-1 peers, adds the staged partial sums to the accumulator fragment in rank
@@ -109,18 +114,30 @@ struct RsPushHooks : HookDefaults {
 };
 
 // ---------------------------------------------------------------------------------------------
-// pull: every tile goes to the own staging matrix; reducer warps sum the tiles this rank owns
+// pull / scatter: the epilogue only stores and signals; reducer warps sum the tiles this rank owns
 // ---------------------------------------------------------------------------------------------
+// A reduce work item is p.rs_sub_rows rows (16 ... 128, a power of two) of a 128-row tile: chosen
+// on the host so that an item always moves about 64 KB (rows x 512 bytes x ws sources) and the last
+// wave of tiles leaves about one item per CTA.
+
 struct RsPullHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
+  __device__ __forceinline__ size_t slab_bytes(const GemmParams& p) const { return (size_t)p.slab_rows * p.rows_c * 2; }
+  // pull: the own staging matrix [M][N]. scatter: slot [rank] of the owner's staging [ws][M/ws][N].
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
+    if (p.rs_algo == 2) {
+      const int owner = (tr * kBM) / p.slab_rows;
+      char* base = (char*)p.bufs[owner] + p.stage_off + (size_t)p.rank * slab_bytes(p);
+      return TileDest{base, (long long)p.rows_c, tr * kBM - owner * p.slab_rows, tc * bn, p.slab_rows, p.rows_c,
+                      p.use_tma_store ? &p.tmap_out[owner] : nullptr};
+    }
     char* base = (char*)p.bufs[p.rank] + p.stage_off;
     return TileDest{base, (long long)p.rows_c, tr * kBM, tc * bn, p.rows_r, p.rows_c, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
-  // counter of 128-row tile `tr`, column tile `tc` in its owner's signal pad
+  // arrival counter of 128-row tile `tr`, column tile `tc` in its owner's signal pad
   __device__ __forceinline__ uint32_t* counter(const GemmParams& p, int owner, int tr, int tc) const {
     return p.pads[owner] + p.flag_base + (size_t)(tr - owner * (p.slab_rows / kBM)) * p.tiles_c + tc;
   }
@@ -133,11 +150,51 @@ struct RsPullHooks : HookDefaults {
     }
     return true;
   }
+  // Where rank s's partial sums of this rank's slab start.
+  __device__ __forceinline__ const char* source_slab(const GemmParams& p, int s) const {
+    if (p.rs_algo == 2) return (const char*)p.bufs[p.rank] + p.stage_off + (size_t)s * slab_bytes(p);
+    return (const char*)p.bufs[s] + p.stage_off + (size_t)p.rank * slab_bytes(p);
+  }
 
-  // Sums 128-row tile (tr, tc) over all ranks into `out`. Thread tid of 128 handles 16-byte
-  // vectors tid, tid + 128, ...: a warp covers one 512-byte row segment per instruction.
-  __device__ __forceinline__ bool reduce_unit(const GemmParams& p, int tr, int tc, int tid, int slot) {
+  // Sum with plain loads: B vectors per thread, all W >= ws ranks' loads of all of them in flight
+  // together; adds in rank order (every call gives the same bits).
+  template <int B, int W>
+  __device__ __forceinline__ void reduce_loads(const GemmParams& p, int tid, int total, int vpr, int lrow0, int col0) {
+    for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * B) {
+      U4 x[B][W];
+#pragma unroll
+      for (int k = 0; k < B; ++k) {
+        const int i = i0 + k * kRsReducerThreads;
+        if (i < total) {
+          const int r = i / vpr, v = i - r * vpr;
+          const size_t off = ((size_t)(lrow0 + r) * p.rows_c + col0 + v * 8) * 2;
+#pragma unroll
+          for (int s = 0; s < W; ++s)
+            if (s < p.ws) x[k][s] = ld16(source_slab(p, s) + off);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < B; ++k) {
+        const int i = i0 + k * kRsReducerThreads;
+        if (i < total) {
+          float f8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int s = 0; s < W; ++s)
+            if (s < p.ws) acc8(x[k][s], f8);
+          const int r = i / vpr, v = i - r * vpr;
+          st16((char*)p.out + ((size_t)(lrow0 + r) * p.ldo + col0 + v * 8) * 2, pack8(f8));
+        }
+      }
+    }
+  }
+
+  // One work item: rows [sub*rs_sub_rows, +rs_sub_rows) of 128-row tile (tr, tc) of the own slab, summed over all
+  // ranks into `out`. Thread tid of 128 handles 16-byte vectors tid, tid + 128, ...: a warp covers
+  // one 512-byte row segment per instruction. The item that finishes a tile last puts the tile's
+  // counters back to zero.
+  __device__ __forceinline__ bool reduce_item(const GemmParams& p, int tr, int tc, int sub, int tid, int slot) {
     uint32_t* f = counter(p, p.rank, tr, tc);
+    uint32_t* done = f + p.rs_done_off;
     const uint32_t need = (uint32_t)p.ws;
     if (tid == 0) {
       trace_put(p, 2, slot, 0);
@@ -148,15 +205,14 @@ struct RsPullHooks : HookDefaults {
     if (!status_ok(p.sync)) return false;
     const int N = p.rows_c;
     const int col0 = tc * bn;
-    const int ncols = min(bn, N - col0);
-    const int vpr = ncols / 8;                       // N % 8 == 0
-    const int rows = min(kBM, p.rows_r - tr * kBM);
+    const int vpr = min(bn, N - col0) / 8;                       // N % 8 == 0
+    const int lrow0 = tr * kBM - p.rank * p.slab_rows + sub * p.rs_sub_rows;
+    const int rows = min(p.rs_sub_rows, p.slab_rows - lrow0);
     const int total = rows * vpr;
-    const size_t g_row0 = (size_t)tr * kBM;
-    const size_t o_row0 = g_row0 - (size_t)p.rank * p.slab_rows;
     if (p.mc_ptr != nullptr) {
-      // in-switch sum: eight 16-byte multimem.ld_reduce in flight per thread
-      constexpr int B = 8;
+      // in-switch sum (pull only)
+      const char* src = (const char*)p.mc_ptr + p.stage_off + (size_t)p.rank * slab_bytes(p) + ((size_t)lrow0 * N + col0) * 2;
+      constexpr int B = 4;
       for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * B) {
         U4 x[B];
 #pragma unroll
@@ -164,7 +220,7 @@ struct RsPullHooks : HookDefaults {
           const int i = i0 + k * kRsReducerThreads;
           if (i < total) {
             const int r = i / vpr, v = i - r * vpr;
-            x[k] = multimem_ld_reduce_bf16x8((const char*)p.mc_ptr + p.stage_off + ((g_row0 + r) * N + col0 + v * 8) * 2);
+            x[k] = multimem_ld_reduce_bf16x8(src + ((size_t)r * N + v * 8) * 2);
           }
         }
 #pragma unroll
@@ -172,79 +228,56 @@ struct RsPullHooks : HookDefaults {
           const int i = i0 + k * kRsReducerThreads;
           if (i < total) {
             const int r = i / vpr, v = i - r * vpr;
-            st16((char*)p.out + ((o_row0 + r) * p.ldo + col0 + v * 8) * 2, x[k]);
+            st16((char*)p.out + ((size_t)(lrow0 + r) * p.ldo + col0 + v * 8) * 2, x[k]);
           }
         }
       }
+    } else if (p.ws <= 2) {
+      reduce_loads<8, 2>(p, tid, total, vpr, lrow0, col0);
+    } else if (p.ws <= 4) {
+      reduce_loads<4, 4>(p, tid, total, vpr, lrow0, col0);
     } else {
-      // peer loads: two vectors per thread with every rank's load in flight; adds in rank order
-      for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * 2) {
-        float f8[2][8];
-        size_t soff[2];
-        bool act[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int i = i0 + k * kRsReducerThreads;
-          act[k] = i < total;
-          const int r = act[k] ? i / vpr : 0, v = act[k] ? i - r * vpr : 0;
-          soff[k] = ((g_row0 + r) * N + col0 + v * 8) * 2;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) f8[k][e] = 0.f;
-        }
-        for (int s0 = 0; s0 < p.ws; s0 += 8) {
-          U4 x[2][8];
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (act[k] && s0 + s < p.ws) x[k][s] = ld16((const char*)p.bufs[s0 + s] + p.stage_off + soff[k]);
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (act[k] && s0 + s < p.ws) acc8(x[k][s], f8[k]);
-        }
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int i = i0 + k * kRsReducerThreads;
-          if (act[k]) {
-            const int r = i / vpr, v = i - r * vpr;
-            st16((char*)p.out + ((o_row0 + r) * p.ldo + col0 + v * 8) * 2, pack8(f8[k]));
-          }
-        }
-      }
+      reduce_loads<2, 8>(p, tid, total, vpr, lrow0, col0);
     }
-    // counter back to zero for the call after next (the next one uses the other bank)
+    reducer_bar_sync();                        // every thread's loads of this item have returned
     if (tid == 0) {
-      red_add_relaxed_sys(f, 0u - need);
+      if (atomicAdd(done, 1u) == (uint32_t)(kBM / p.rs_sub_rows - 1)) {
+        *done = 0u;
+        red_add_relaxed_sys(f, 0u - need);     // zero again for the call after next (the next uses the other bank)
+      }
       trace_put(p, 2, slot, 2);
     }
     return true;
   }
 
-  // Reducer warps: walk the tile order, count the tiles of the own slab and serve every
-  // num_workers-th of them (a CTA pair: each CTA its own 128-row half).
+  // Reducer warps: walk the tile order, number the work items of the own slab's tiles in that
+  // order (a pair tile: upper half first) and serve every num_ctas-th of them.
   __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
     const int total = p.tiles_r * p.tiles_c;
     const int rows_per_tile = half < 0 ? kBM : 2 * kBM;
-    unsigned own = 0;
+    const unsigned halves = half < 0 ? 1u : 2u;
+    const unsigned me = half < 0 ? worker : 2u * worker + (unsigned)half;
+    const unsigned num_ctas = num_workers * halves;
+    const unsigned subs = (unsigned)(kBM / p.rs_sub_rows);
+    const unsigned per_tile = halves * subs;
+    unsigned base = 0;                         // number of the first work item of the current own tile
     int served = 0;
     for (int t = 0; t < total; ++t) {
       int trv, tc;
       tile_coords(p, t, trv, tc);
       if ((trv * rows_per_tile) / p.slab_rows != p.rank) continue;
-      const bool mine = (own % num_workers) == worker;
-      ++own;
-      if (!mine) continue;
-      const int tr = half < 0 ? trv : 2 * trv + half;
-      if (tr * kBM >= p.rows_r) continue;
-      if (!reduce_unit(p, tr, tc, tid, served++)) return;
+      for (unsigned k = (me + num_ctas - base % num_ctas) % num_ctas; k < per_tile; k += num_ctas) {
+        const int tr = half < 0 ? trv : 2 * trv + (int)(k / subs);
+        if (tr * kBM >= p.rows_r) continue;
+        if (!reduce_item(p, tr, tc, (int)(k % subs), tid, served++)) return;
+      }
+      base += per_tile;
     }
   }
 };
 
 // ---------------------------------------------------------------------------------------------
-// kernels: ALGO 0 push (192 threads), 1 pull (192 + 128 reducer threads)
+// kernels: ALGO 0 push (192 threads), 1 pull / scatter (192 + 128 reducer threads)
 // ---------------------------------------------------------------------------------------------
 template <int ALGO>
 __device__ __forceinline__ void rs_body(const GemmParams& p, unsigned bid, unsigned nb) {
@@ -306,6 +339,7 @@ struct RsPlan {
   int group_r, pivot_r, interleave_r;
   int workers;         // CTA pairs (pair) or CTAs that walk the tile order
   int grid;            // CTAs launched
+  int sub_rows;        // pull / scatter: rows of a reduce work item
 };
 
 // Tiling and tile order of the fused reduce-scatter GEMM; one function for the launcher and for
@@ -336,6 +370,8 @@ static int rs_plan(int M, int N, int ws, int rank, int algo, unsigned cap, bool 
     if (g > pl->tiles_r) g = pl->tiles_r;
   }
   pl->group_r = g;
+  pl->sub_rows = kBM;
+  while (pl->sub_rows > 16 && pl->sub_rows * ws > kBM) pl->sub_rows /= 2;   // about 128 / ws, at least 16
   const unsigned tiles = (unsigned)pl->tiles_r * (unsigned)pl->tiles_c;
   if (pl->pair) {
     unsigned pairs = tiles < cap / 2 ? tiles : cap / 2;
@@ -364,7 +400,7 @@ KR_API int kr_gemm_rs_set_trace(unsigned long long* buf, unsigned long long word
   return KR_SUCCESS;
 }
 
-// out[0..7] = {pair, tiles_r, tiles_c, group_r, pivot_r, interleave_r, workers, grid} for the
+// out[0..8] = {pair, tiles_r, tiles_c, group_r, pivot_r, interleave_r, workers, grid, sub_rows} for the
 // given problem on a device with `num_ctas` CTAs available. For tests of the flag protocol.
 KR_API int kr_rs_plan(int M, int N, int ws, int rank, int algo, int num_ctas, int allow_pair, int* out) {
   RsPlan pl;
@@ -372,16 +408,17 @@ KR_API int kr_rs_plan(int M, int N, int ws, int rank, int algo, int num_ctas, in
   if (rc) return rc;
   out[0] = pl.pair; out[1] = pl.tiles_r; out[2] = pl.tiles_c; out[3] = pl.group_r;
   out[4] = pl.pivot_r; out[5] = pl.interleave_r; out[6] = pl.workers; out[7] = pl.grid;
+  out[8] = pl.sub_rows;
   return KR_SUCCESS;
 }
 
 // Fused GEMM -> reduce-scatter. a[M, K_local], bt[N, K_local]; out[M/ws, N] bf16.
 // bufs[r] = rank r's staging workspace (bufs: device table; bufs_host: the same addresses in host
-// memory, used to describe staging to TMA, or nullptr): push needs M*N*2 bytes, pull 2*M*N*2
-// (two halves, alternating with call_parity) and DEDICATED to this op. mc_ptr: multicast address of
-// the staging workspace or nullptr (pull then sums with peer loads). algo: 0 push, 1 pull.
-// Tile counters live in the signal pads from word flag_base on (zero on entry, zero again after
-// the call); pull uses the bank selected by call_parity.
+// memory, used to describe staging to TMA, or nullptr): push needs M*N*2 bytes, pull and scatter
+// 2*M*N*2 (two halves, alternating with call_parity) and DEDICATED to this op. mc_ptr: multicast
+// address of the staging workspace (pull then sums in the NVSwitch) or nullptr (peer loads).
+// algo: 0 push, 1 pull, 2 scatter. Tile counters live in the signal pads from word flag_base on
+// (zero on entry, zero again after the call); pull and scatter use the bank selected by call_parity.
 KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads, void* mc_ptr, int rank,
                            int ws, const void* a, long long lda, const void* bt, long long ldb, void* out,
                            long long ldo, int M, int N, int K, int algo, int call_parity, uint32_t pad_base,
@@ -389,12 +426,12 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
                            cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
-  KR_REQUIRE(algo == 0 || algo == 1, "algo must be 0 (push) or 1 (pull)");
+  KR_REQUIRE(algo >= 0 && algo <= 2, "algo must be 0 (push), 1 (pull) or 2 (scatter)");
   KR_REQUIRE(pad_base % (ws > 0 ? ws : 1) == 0, "pad_base must be a multiple of the world size");
   KR_REQUIRE(ldo % 8 == 0 && ((uintptr_t)out & 15) == 0, "output rows must be 16-byte aligned");
   const unsigned cap = grid_cap(d);
   RsPlan pl;
-  int rc = rs_plan(M, N, ws, rank, algo, cap, pair_enabled() && !emu_recorder().active, &pl);
+  int rc = rs_plan(M, N, ws, rank, algo == 0 ? 0 : 1, cap, pair_enabled() && !emu_recorder().active, &pl);
   if (rc) return rc;
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -430,14 +467,24 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
     }
   } else {
     const unsigned long long half = staging_bytes / 2 / 1024 * 1024;
-    KR_REQUIRE(half >= mn2, "staging workspace too small (pull needs 2 * M * N * 2 bytes)");
+    KR_REQUIRE(half >= mn2, "staging workspace too small (pull and scatter need 2 * M * N * 2 bytes)");
+    KR_REQUIRE(pad_words > flag_base, "signal pad too small for the tile counters");
     const unsigned long long bank = (pad_words - flag_base) / 2;
-    KR_REQUIRE(pad_words > flag_base && units <= bank, "signal pad too small for the tile counters");
+    KR_REQUIRE(2 * units <= bank, "signal pad too small for the tile counters");
     p.stage_off = (call_parity & 1) ? half : 0;
     p.flag_base = flag_base + ((call_parity & 1) ? (uint32_t)bank : 0u);
-    p.mc_ptr = mc_ptr;
-    if (bufs_host != nullptr)
+    p.rs_done_off = (uint32_t)units;           // per tile: [arrivals][work items done]
+    p.rs_sub_rows = pl.sub_rows;
+    p.mc_ptr = algo == 1 ? mc_ptr : nullptr;
+    if (bufs_host != nullptr && algo == 1) {
       p.use_tma_store = store_tmap((const char*)bufs_host[rank] + p.stage_off, M, N, N, &p.tmap_out[0]) ? 1 : 0;
+    } else if (bufs_host != nullptr && ws <= 8) {
+      bool ok = true;
+      for (int o = 0; o < ws && ok; ++o)
+        ok = store_tmap((const char*)bufs_host[o] + p.stage_off + (size_t)rank * p.slab_rows * N * 2, p.slab_rows, N, N,
+                        &p.tmap_out[o]);
+      p.use_tma_store = ok ? 1 : 0;
+    }
   }
   p.tiles_r = pl.tiles_r;
   p.tiles_c = pl.tiles_c;
@@ -455,7 +502,7 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
     // each CTA of a pair loads its own 128 rows of the column operand: box of 128 rows, not 256
     rc = get_tmap(p.host_c_ptr, p.rows_c, p.K, p.host_ldc, 128, &p.tmap_c);
     if (rc) return rc;
-    const void* fn = algo == 0 ? (const void*)gemm_rs_push_pair_kernel : (const void*)gemm_rs_pull_pair_kernel;
+    const void* fn = algo == 0 ? (const void*)gemm_rs_push_pair_kernel : (const void*)gemm_rs_pull_pair_kernel;   // pull kernel also runs scatter
     rc = ensure_dynamic_smem(fn, PairCfg::SMEM);
     if (rc) return rc;
     void* args[] = {(void*)&p};

@@ -78,6 +78,10 @@ struct alignas(64) GemmParams {
   uint32_t* progress;        // [ws * splits] chunk flags
   uint32_t* counters;        // [ws * splits] arrival counters (zeroed, self-resetting)
   int splits, shard_rows, chunk_rows;
+  const void* ag_shard;      // push: this rank's own shard [shard_rows, K]
+  int ag_push;               // 1: every rank pushes its shard into the peers' gathered buffers (comm CTAs)
+  int ag_entry_barrier;      // push into a caller-owned symmetric a_out: wait until every rank has entered
+  unsigned long long ag_out_off;   // push: byte offset of the gathered buffer inside bufs[r]
   // AR (decode): byte offsets inside every rank's staging buffer and the second flag bank
   int ar_algo;               // 0: one-shot pull, 1: two-shot (tile owner reduces and publishes)
   unsigned long long stage_off;   // one-shot: this call's staging (alternates between two halves)
@@ -87,7 +91,9 @@ struct alignas(64) GemmParams {
   void* mc_ptr;                   // multicast address of the staging buffer (NVLS) or nullptr
   // RS
   int slab_rows;             // M / ws
-  int rs_algo;               // 0: push partial tiles to the owner; 1: owner pulls and reduces (NVLS or peer loads)
+  int rs_algo;               // 0: push, owner reduces in its epilogue; 1: pull; 2: scatter (push + reducer warps)
+  int rs_sub_rows;           // pull / scatter: rows of one reduce work item (power of two, 16 ... 128)
+  uint32_t rs_done_off;      // pull / scatter: words from a tile's arrival counter to its "items done" counter
   SyncCtx sync;
   // optional per-tile timeline (nullptr: off): [CTA][role][tile slot][field] %globaltimer stamps
   unsigned long long* trace;

@@ -11,12 +11,15 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_GEMM_PAIR``        ``0`` forces the single-CTA GEMM kernel (default: CTA pairs when eligible)
 ``KRAKEN_GEMM_GROUP``       row tiles per column sweep of the GEMM tile order (default 16)
 ``KRAKEN_TMA_STORE``        ``0`` makes the GEMM epilogue use vector stores instead of TMA stores
-``KRAKEN_AG_MODE``          ``ce`` (copy engines + stream flags feed the GEMM kernel, default) or ``sm`` (comm CTAs
-                            inside the GEMM kernel pull the shards)
-``KRAKEN_RS_ALGO``          ``pull`` (default: owners sum the ranks' staged tiles, in the NVSwitch when possible) or
-                            ``push`` (partial tiles are pushed to the owner and summed in its epilogue)
+``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``push`` (default: comm CTAs write the own shard into
+                            the peers' gathered buffers), ``ce`` (copy engines + stream flags) or ``sm`` (comm CTAs
+                            pull the peers' shards)
+``KRAKEN_RS_ALGO``          ``pull`` (reducer warps sum the ranks' staged tiles with peer loads), ``scatter`` (tiles are
+                            stored into the owner's staging, reducer warps sum local memory) or ``push`` (tiles
+                            are stored into the owner's staging and summed in its epilogue)
 ``KRAKEN_ONE_SHOT``         ``push`` (default: small one-shot all-reduces write into the peers' workspace and meet in
                             one barrier) or ``pull`` (copy-in, barrier, remote loads, exit barrier)
+``KRAKEN_RS_NVLS``          ``1``: the pull reduce-scatter sums with ``multimem.ld_reduce`` (default 0: peer loads)
 ``KRAKEN_NVTX``             ``1`` wraps every public op in an NVTX range named after it (for timeline tools)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)
@@ -61,18 +64,25 @@ def num_comm_sms() -> int:
 
 
 def ag_mode() -> str:
-    v = os.environ.get("KRAKEN_AG_MODE", "ce").strip().lower()
-    return v if v in ("sm", "ce") else "ce"
+    v = os.environ.get("KRAKEN_AG_MODE", "push").strip().lower()
+    return v if v in ("push", "sm", "ce") else "push"
 
 
 def rs_algo() -> str:
     v = os.environ.get("KRAKEN_RS_ALGO", "pull").strip().lower()
-    return v if v in ("pull", "push") else "pull"
+    return v if v in ("pull", "push", "scatter") else "pull"
 
 
 def one_shot_mode() -> str:
     v = os.environ.get("KRAKEN_ONE_SHOT", "push").strip().lower()
     return v if v in ("push", "pull") else "push"
+
+
+def rs_nvls() -> bool:
+    """Whether the pull reduce-scatter sums in the NVSwitch (multimem.ld_reduce) instead of with
+    peer loads. Off by default: measured at 2 GPUs, 16-byte multimem.ld_reduce requests delivered
+    about 90 GB/s per GPU next to a running GEMM, far below what peer loads reach."""
+    return os.environ.get("KRAKEN_RS_NVLS", "0") == "1"
 
 
 def dump_kernel() -> bool:

@@ -61,7 +61,7 @@ def _zero_counters(device: torch.device, n: int, emu) -> torch.Tensor:
 
 
 def _default_comm_ctas(n_local: int, ws: int) -> int:
-    """Comm CTAs of the fused all-gather GEMM. The first remote shard must land by the time the MMA
+    """Comm CTAs of the in-kernel PULL engine. The first remote shard must land by the time the MMA
     CTAs finish the local one, which needs M*K*2 bytes per GEMM time = (tensor rate) / N_local bytes
     per second whatever the world size; one comm CTA was measured to pull about 15 GB/s over NVLink
     (its copies in flight cover only a fraction of the link's latency-bandwidth product).
@@ -78,16 +78,42 @@ def _default_comm_ctas(n_local: int, ws: int) -> int:
     return max(2, min(32, n))
 
 
+def _default_push_ctas(shard_bytes: int, ws: int, flops: float) -> int:
+    """Comm CTAs of the PUSH engine: each rank writes ws copies of its shard (ws - 1 over NVLink)
+    during the GEMM; a comm CTA streams local memory -> shared memory -> peer with posted bulk
+    stores, taken as 60 GB/s. KRAKEN_NUM_COMM_SMS overrides."""
+    import os
+
+    if "KRAKEN_NUM_COMM_SMS" in os.environ:
+        return config.num_comm_sms()
+    t_gemm = flops / 1.45e15
+    rate = ws * shard_bytes / max(t_gemm, 1e-6)
+    n = int(-(-rate // 60e9))
+    n = (n + 1) & ~1
+    return max(2, min(16, n))
+
+
+_AG_FLAG_BANK = 2048      # chunk flags per bank in the signal pad (two banks from TILE_FLAG_BASE on)
+
+
 def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tensor | None = None,
                       progress: torch.Tensor | None = None, **kwargs) -> tuple[torch.Tensor, torch.Tensor]:
     """(gathered A [M, K], C [M, N] = gathered A @ b). `a_shared` is this rank's [M/ws, K] shard in
     symmetric memory. The persistent tcgen05 GEMM starts on the local shard (rank pivot) and
-    consumes remote chunks as their `progress` flags appear. Two engines fill `a_out` and raise the
-    flags: backend="ce" (default) — copy engines on a backend stream, one stream memory operation
-    per chunk, no SM spent on communication (measured fastest: a remote pull needs megabytes in
-    flight to cover NVLink latency, which a handful of CTAs cannot hold); backend="sm" — comm CTAs
-    inside the same kernel launch pull the shards with bulk async copies (single launch, no second
-    stream). kwargs: splits_per_rank=1, num_comm_sms, backend, group."""
+    consumes remote chunks as their flags appear. Engines that move the shards (kwarg ``backend``):
+
+    * ``"push"`` (default): comm CTAs of the same launch write this rank's shard into every peer's
+      gathered buffer with posted bulk stores — first to the rank that needs it first — and raise
+      the chunk's flag in that peer's signal pad. One launch, no barrier, no second stream. The
+      gathered buffer must be symmetric: with ``a_out=None`` the op returns a view of a
+      double-buffered library workspace, valid until the second next call on the same group; a
+      symmetric ``a_out`` is written in place (at the price of an entry barrier); an ordinary
+      ``a_out`` receives a device copy of the workspace afterwards.
+    * ``"ce"``: copy engines on a backend stream, one stream memory operation per chunk (the
+      reference's recipe, kraken/fused/all_gather_matmul.py:296-304).
+    * ``"sm"``: comm CTAs pull the peers' shards with bulk async copies.
+
+    kwargs: splits_per_rank=1, num_comm_sms, backend, group."""
     group = kwargs.get("group")
     if a_shared.device.type != "cuda":
         a, c = ref.all_gather_matmul(a_shared, b, group)
@@ -110,40 +136,73 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     splits = int(kwargs.get("splits_per_rank", 1))
     if shard_rows % splits:
         splits = 1
-    if a_out is None:
-        a_out = torch.empty((M, K), dtype=a_shared.dtype, device=a_shared.device)
-    if progress is None:
-        progress = torch.zeros(ws * splits, dtype=torch.uint32, device=a_shared.device)
-    else:
-        progress.zero_()
-    c = torch.empty((M, N), dtype=a_shared.dtype, device=a_shared.device)
+    dev = a_shared.device
     backend = kwargs.get("backend", config.ag_mode())
-    counters = _zero_counters(a_shared.device, ws * splits, hdl.group.emu)
+    if backend not in ("push", "ce", "sm"):
+        raise ValueError("backend must be 'push', 'ce' or 'sm'")
+    emu = hdl.group.emu
+    if backend == "ce" and (emu is not None or ws == 1):
+        backend = "sm"
+    if backend == "push" and (ws == 1 or ws * splits > _AG_FLAG_BANK):
+        backend = "sm"
+    if hdl.offset_of(a_shared):
+        raise ValueError("a_shared must start at the beginning of its symmetric buffer")
+    c = torch.empty((M, N), dtype=a_shared.dtype, device=dev)
+    counters = _zero_counters(dev, ws * splits + 1, emu)
     L = _lib.lib()
     _log.log_kernel_choice("all_gather_matmul", f"M={M} N={N} K={K} ws={ws} splits={splits} engine={backend}")
-    off = hdl.offset_of(a_shared)
-    if off:
-        raise ValueError("a_shared must start at the beginning of its symmetric buffer")
-    if ws == 1 and hdl.group.emu is None:
+    stream = _lib.current_stream_ptr()
+    if progress is not None:
+        progress.zero_()
+
+    if backend == "push":
+        user_out = a_out
+        if a_out is not None and symm_mem.is_symm_tensor(a_out):
+            oh = symm_mem.rendezvous(a_out, group)            # caller-owned symmetric buffer: written in place
+            off, gathered, barrier, user_out = oh.offset_of(a_out), a_out, 1, None
+        else:
+            half = -(-M * K * 2 // 1024) * 1024
+            oh = symm_mem.get_symm_mem_workspace(group, 2 * half, dev, kind="ag_out")
+            barrier = 0
+            off = None
+        calls = getattr(oh, "_ag_calls", 0)
+        oh._ag_calls = calls + 1
+        if off is None:
+            off = (calls & 1) * half
+            gathered = oh.get_buffer(rank, (M, K), torch.bfloat16, storage_offset=off // 2)
+        n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_push_ctas(shard_rows * K * 2, ws, 2.0 * M * N * K)
+        _lib.check(L.kr_ag_gemm_bf16(oh.buffer_ptrs_dev, oh.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
+                                     gathered.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
+                                     progress.data_ptr() if progress is not None else None, counters.data_ptr(), n_comm,
+                                     0, 1, off, config.TILE_FLAG_BASE + (calls & 1) * _AG_FLAG_BANK, oh.signal_pad_words,
+                                     barrier, stream))
+        if user_out is not None:
+            user_out.copy_(gathered)
+            gathered = user_out
+        return gathered, c
+
+    if a_out is None:
+        a_out = torch.empty((M, K), dtype=a_shared.dtype, device=dev)
+    if progress is None:
+        progress = torch.zeros(ws * splits, dtype=torch.uint32, device=dev)
+    args_tail = (0, 0, 0, 0, 0, stream)     # pad_base, then the push arguments (unused)
+    if ws == 1 and emu is None:
         # nothing to gather: a device copy fills a_out while the GEMM reads the shard in place
         a_out.copy_(a_shared)
         progress.fill_(1)
-        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
-                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
-                                     progress.data_ptr(), counters.data_ptr(), -1, 0, _lib.current_stream_ptr()))
-    elif backend == "ce" and hdl.group.emu is None and ws > 1:
+        n_comm = -1
+    elif backend == "ce":
         from ..comm.all_gather import _copy_engine_all_gather_w_progress
 
-        stream = _copy_engine_all_gather_w_progress(a_out, a_shared, progress, splits)
-        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
-                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
-                                     progress.data_ptr(), counters.data_ptr(), -1, 0, _lib.current_stream_ptr()))
-        torch.cuda.current_stream().wait_stream(stream)
+        ce_stream = _copy_engine_all_gather_w_progress(a_out, a_shared, progress, splits)
+        n_comm = -1
     else:
         n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_comm_ctas(N, ws)
-        _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
-                                     a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
-                                     progress.data_ptr(), counters.data_ptr(), n_comm, 0, _lib.current_stream_ptr()))
+    _lib.check(L.kr_ag_gemm_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
+                                 a_out.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
+                                 progress.data_ptr(), counters.data_ptr(), n_comm, 0, *args_tail))
+    if backend == "ce" and n_comm == -1 and ws > 1:
+        torch.cuda.current_stream().wait_stream(ce_stream)
     return a_out, c
 
 
@@ -185,15 +244,17 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
 
 
 def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
-    """[M/ws, N] = reduce_scatter(a @ b) along M, in one kernel. Two exchange algorithms:
-    "pull" (default) — every rank TMA-stores its partial tiles into its own symmetric staging and
-    bumps a per-tile counter at the tile's owner; reducer warps inside the same kernel sum each owned
-    tile over all ranks (``multimem.ld_reduce`` in the NVSwitch, or peer loads in rank order) as soon
-    as all ranks have stored it, while the MMAs of later tiles run; "push" — the epilogue TMA-stores
-    remote tiles into the owner's staging slab over NVLink and the owner adds them to its accumulator
-    in the epilogue of its own tiles (computed last). Both are bit-reproducible from call to call.
+    """[M/ws, N] = reduce_scatter(a @ b) along M, in one kernel. Three exchange algorithms:
+    "pull" — every rank TMA-stores its partial tiles into its own symmetric staging and bumps a
+    per-tile counter at the tile's owner; reducer warps inside the same kernel sum each owned tile
+    over all ranks (peer loads in rank order, or ``multimem.ld_reduce`` with KRAKEN_RS_NVLS=1) as
+    soon as all ranks have stored it, while the MMAs of later tiles run; "scatter" — the same, but
+    the epilogue TMA-stores each tile into the owner's staging over NVLink so the reducer warps sum
+    local memory; "push" — the epilogue TMA-stores remote tiles into the owner's staging slab and
+    the owner adds them to its accumulator in the epilogue of its own tiles (computed last). All
+    are bit-reproducible from call to call.
     Shapes whose slab is not a multiple of 128 rows, or N < 256, run GEMM -> symmetric staging ->
-    reduce-scatter kernel. kwargs: group, algo="pull"|"push" (default KRAKEN_RS_ALGO)."""
+    reduce-scatter kernel. kwargs: group, algo="pull"|"scatter"|"push" (default KRAKEN_RS_ALGO)."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_reduce_scatter(a, b, group)
@@ -209,8 +270,8 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
         raise ValueError("M must be divisible by the world size")
     out = torch.empty((M // ws, N), dtype=torch.bfloat16, device=a.device)
     algo = str(kwargs.get("algo", config.rs_algo()))
-    if algo not in ("pull", "push"):
-        raise ValueError("algo must be 'pull' or 'push'")
+    if algo not in ("pull", "push", "scatter"):
+        raise ValueError("algo must be 'pull', 'scatter' or 'push'")
     fused_ok = (M // ws) % 128 == 0 and N % 8 == 0 and N >= 256
     force = bool(kwargs.get("_force_fused", False))           # tests: run the fused kernel at world size 1
     if _log.dump_enabled():
@@ -222,16 +283,17 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
     if ws == 1 and not (force and fused_ok):
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, s))
     elif fused_ok:
-        if algo == "pull":
+        if algo in ("pull", "scatter"):
             hdl = symm_mem.get_symm_mem_workspace(group, 2 * M * N * 2 + 2048, a.device, kind="gemm_rs")
             calls = getattr(hdl, "_gemm_rs_calls", 0)        # per staging buffer: selects the half / counter bank
             hdl._gemm_rs_calls = calls + 1
         else:
             hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
             calls = 0
+        mc = hdl.multicast_ptr if (algo == "pull" and config.rs_nvls()) else 0
         _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev,
-                                     hdl.multicast_ptr or None, hdl.rank, ws, a2.data_ptr(), lda, bt.data_ptr(), ldb,
-                                     out.data_ptr(), N, M, N, K, 1 if algo == "pull" else 0, calls & 1, 0,
+                                     mc or None, hdl.rank, ws, a2.data_ptr(), lda, bt.data_ptr(), ldb,
+                                     out.data_ptr(), N, M, N, K, {"push": 0, "pull": 1, "scatter": 2}[algo], calls & 1, 0,
                                      config.TILE_FLAG_BASE, hdl.signal_pad_words, hdl.buffer_size, s))
     else:
         if (M * N) % (8 * ws):

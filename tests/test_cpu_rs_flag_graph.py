@@ -6,8 +6,9 @@ Every worker (a CTA, or a CTA pair) of every rank walks its tiles in order. The 
 push   a remote tile's signal to its owner is sent one tile late (the TMA-store epilogue defers
        the completion hook); an own-slab tile first waits for ws-1 signals from the peers. With
        ``flush_before_wait`` the held-back signal is sent before any wait, as the kernels do.
-pull   no epilogue ever waits; every tile (own ones too) signals its owner, one tile late, and the
-       reducer warps of the owner's workers wait for ws signals per owned tile.
+pull   (and scatter) no epilogue ever waits; every tile (own ones too) signals its owner, one tile
+       late; each owned tile is cut into work items dealt round-robin to the owner's CTAs, whose
+       reducer warps wait for the tile's ws signals.
 
 The model runs to a fixed point; a worker that can never advance is a deadlock. The cases include
 the shapes of the tensor-parallel MLP benchmark (M 2048 and 8192, N 8192) at 2, 4 and 8 ranks on 74
@@ -21,9 +22,9 @@ from kraken_b200.ops import lib as klib
 
 
 def _plan(M, N, ws, rank, algo, ctas, pair):
-    out = (ctypes.c_int * 8)()
+    out = (ctypes.c_int * 9)()
     klib.check(klib.lib().kr_rs_plan(M, N, ws, rank, algo, ctas, 1 if pair else 0, out))
-    keys = ["pair", "tiles_r", "tiles_c", "group_r", "pivot_r", "interleave_r", "workers", "grid"]
+    keys = ["pair", "tiles_r", "tiles_c", "group_r", "pivot_r", "interleave_r", "workers", "grid", "sub_rows"]
     return dict(zip(keys, list(out)))
 
 
@@ -81,31 +82,45 @@ def simulate_push(M, N, ws, ctas, pair, flush_before_wait):
 
 
 def simulate_pull(M, N, ws, ctas, pair):
-    """Returns (stuck reducers, owned tiles never reduced)."""
+    """Pull and scatter share this protocol. Returns (work items whose tile never got all ws
+    signals, work items served by no CTA or by more than one)."""
     plans = [_plan(M, N, ws, r, 1, ctas, pair) for r in range(ws)]
     orders = [_order(pl) for pl in plans]
     assert all(o == orders[0] for o in orders)            # every rank walks the same order
-    rows_per_tile = 256 if plans[0]["pair"] else 128
+    is_pair = bool(plans[0]["pair"])
+    rows_per_tile = 256 if is_pair else 128
     slab_tiles = (M // ws) // rows_per_tile
-    W = plans[0]["workers"]
+    halves = 2 if is_pair else 1
+    num_ctas = plans[0]["workers"] * halves
+    SUBS = 128 // plans[0]["sub_rows"]                     # work items per 128-row tile
+    assert plans[0]["sub_rows"] in (16, 32, 64, 128) and plans[0]["sub_rows"] * min(ws, 8) >= 128
+    per_tile = halves * SUBS
     flags = {}
     for r in range(ws):                                   # epilogues never wait: all signals get sent
         for (tr, tc) in orders[r]:
-            key = (tr // slab_tiles, (tr, tc))
-            flags[key] = flags.get(key, 0) + 1
-    stuck = missing = 0
+            for h in range(halves):
+                key = (tr // slab_tiles, (tr * halves + h, tc))
+                flags[key] = flags.get(key, 0) + 1
+    starved = wrong = 0
     for r in range(ws):
-        own = [t for t in orders[r] if t[0] // slab_tiles == r]
-        assert len(own) == slab_tiles * plans[r]["tiles_c"]
-        served = set()
-        for w in range(W):
-            for t in own[w::W]:
-                if flags.get((r, t), 0) != ws:
-                    stuck += 1
-                    break
-                served.add(t)
-        missing += len(own) - len(served)
-    return stuck, missing
+        served = {}
+        for me in range(num_ctas):                        # the arithmetic of the reducer warps' loop
+            base = 0
+            for (tr, tc) in orders[r]:
+                if tr // slab_tiles != r:
+                    continue
+                k = (me + num_ctas - base % num_ctas) % num_ctas
+                while k < per_tile:
+                    item = (tr * halves + k // SUBS, tc, k % SUBS)
+                    served[item] = served.get(item, 0) + 1
+                    if flags.get((r, item[:2]), 0) != ws:
+                        starved += 1
+                    k += num_ctas
+                base += per_tile
+        own_tiles = [t for t in orders[r] if t[0] // slab_tiles == r]
+        expect = {(tr * halves + h, tc, j) for (tr, tc) in own_tiles for h in range(halves) for j in range(SUBS)}
+        wrong += len(expect.symmetric_difference(served.keys())) + sum(1 for v in served.values() if v != 1)
+    return starved, wrong
 
 
 CASES = [(ws, M, N, ctas, pair)
@@ -130,7 +145,7 @@ def test_model_finds_the_cycle_when_signals_are_held_across_a_wait(ws):
 
 
 @pytest.mark.parametrize("ws,M,N,ctas,pair", CASES)
-def test_pull_every_owned_tile_is_reduced_exactly_once(ws, M, N, ctas, pair):
+def test_pull_every_work_item_is_served_exactly_once(ws, M, N, ctas, pair):
     assert simulate_pull(M, N, ws, ctas, pair) == (0, 0)
 
 

@@ -107,9 +107,10 @@ def test_gemm_persistent_many_tiles_per_cta():
 
 
 # ---- fused GEMM + collective, emulated ranks ---------------------------------------------------
-@pytest.mark.parametrize("ws", [1, 2, 4])
-@pytest.mark.parametrize("splits", [1, 2])
-def test_all_gather_matmul(ws, splits):
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [1, 2, 4])
+@pytest.mark.parametrize("backend", ["push", "sm"])
+def test_all_gather_matmul(ws, splits, backend):
     world = EmuWorld(ws)
     shard_rows, K, N = 256, 512, 384
     g = torch.Generator().manual_seed(6)
@@ -120,10 +121,10 @@ def test_all_gather_matmul(ws, splits):
         ts[r].copy_(shards[r])
     a_full = torch.cat(shards, 0)
     ref = a_full.float() @ bt.float().t()
-    for _ in range(2):
+    for _ in range(3):          # three calls: both gathered-buffer halves / flag banks, then the first again
         progs = [torch.zeros(ws * splits, dtype=torch.uint32, device="cuda") for _ in range(ws)]
         outs = world.run(lambda r: fused.all_gather_matmul(ts[r], bt.t(), progress=progs[r], splits_per_rank=splits,
-                                                           num_comm_sms=4))
+                                                           num_comm_sms=4, backend=backend))
         for r in range(ws):
             ag, c = outs[r]
             assert torch.equal(ag, a_full)
@@ -131,8 +132,35 @@ def test_all_gather_matmul(ws, splits):
             assert bool((progs[r].to(torch.int64) != 0).all())
 
 
+@pytest.mark.parametrize("symmetric_out", [True, False])
+def test_all_gather_matmul_push_into_caller_buffers(symmetric_out):
+    # a caller-owned symmetric a_out is written in place (entry barrier); an ordinary one gets a copy
+    ws = 4
+    world = EmuWorld(ws)
+    shard_rows, K, N = 384, 256, 520
+    g = torch.Generator().manual_seed(16)
+    shards = [torch.randn(shard_rows, K, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+    bt = (0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16).cuda()
+    ts = world.symmetric((shard_rows, K), torch.bfloat16)
+    for r in range(ws):
+        ts[r].copy_(shards[r])
+    outs_buf = world.symmetric((ws * shard_rows, K), torch.bfloat16) if symmetric_out else \
+        [torch.empty(ws * shard_rows, K, dtype=torch.bfloat16, device="cuda") for _ in range(ws)]
+    a_full = torch.cat(shards, 0)
+    ref = a_full.float() @ bt.float().t()
+    for _ in range(2):
+        for o in outs_buf:
+            o.zero_()
+        outs = world.run(lambda r: fused.all_gather_matmul(ts[r], bt.t(), a_out=outs_buf[r], backend="push", num_comm_sms=2))
+        for r in range(ws):
+            ag, c = outs[r]
+            assert ag.data_ptr() == outs_buf[r].data_ptr()
+            assert torch.equal(ag, a_full)
+            _close(c, ref, K)
+
+
 @pytest.mark.parametrize("ws", [2, 4, 8])
-@pytest.mark.parametrize("algo", ["pull", "push"])
+@pytest.mark.parametrize("algo", ["pull", "scatter", "push"])
 def test_gemm_reduce_scatter_fused(ws, algo):
     world = EmuWorld(ws)
     M, N, Kl = 128 * ws * 2, 512, 256
@@ -146,7 +174,7 @@ def test_gemm_reduce_scatter_fused(ws, algo):
             torch.testing.assert_close(outs[r].float(), full[r * (M // ws):(r + 1) * (M // ws)], atol=6e-2, rtol=3e-2)
 
 
-@pytest.mark.parametrize("algo", ["pull", "push"])
+@pytest.mark.parametrize("algo", ["pull", "scatter", "push"])
 def test_gemm_reduce_scatter_fused_several_tiles_per_cta(algo):
     # 4 ranks x 37 CTAs, 16 x 5 tiles of 128 x 256 (last column tile ragged): every CTA walks two or
     # three tiles, owners interleaved (pull) or slab after slab (push)
@@ -168,7 +196,7 @@ def test_gemm_reduce_scatter_fused_several_tiles_per_cta(algo):
             assert all(torch.equal(x, y) for x, y in zip(first, outs))      # bit-reproducible
 
 
-@pytest.mark.parametrize("algo", ["pull", "push"])
+@pytest.mark.parametrize("algo", ["pull", "scatter", "push"])
 @pytest.mark.parametrize("M,N,K", [(2048, 2048, 512), (4096, 1032, 256), (512, 256, 64)])
 def test_gemm_reduce_scatter_kernel_at_world_size_one(algo, M, N, K):
     # the fused kernels (CTA pairs, reducer warps, counters, staging halves) on one real rank

@@ -120,9 +120,9 @@ def _all_ops(rank, ws):
     dist.all_gather(parts, a_sh)
     a_full = torch.cat(parts, 0)
     gold_c = a_full.float() @ bt.float().t()
-    for backend in ("sm", "ce"):
-        for splits in (1, 2):
-            for _ in range(2):
+    for backend in ("push", "sm", "ce"):
+        for splits in (1, 2, 4):
+            for _ in range(3):
                 ag, c = fused.all_gather_matmul(a_sh, bt.t(), splits_per_rank=splits, backend=backend)
                 torch.cuda.synchronize()
                 assert torch.equal(ag, a_full), (backend, splits)
@@ -137,6 +137,7 @@ def _all_ops(rank, ws):
         ms = M // ws
         gold_rs = full[rank * ms:(rank + 1) * ms]
         variants = [lambda: fused.gemm_reduce_scatter(a, bt2.t(), algo="pull"),
+                    lambda: fused.gemm_reduce_scatter(a, bt2.t(), algo="scatter"),
                     lambda: fused.gemm_reduce_scatter(a, bt2.t(), algo="push"),
                     lambda: fused.gemm_reduce_scatter_ce_persistent(a, bt2.t())]
         for fn in variants:
