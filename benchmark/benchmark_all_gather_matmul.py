@@ -2,7 +2,9 @@
 bf16 [M/ws, K], B bf16 [K, N/ws] column-major (b.T contiguous). Backends: this library's fused
 kernel (in-kernel pull and copy-engine engines), NCCL all_gather + cuBLAS, torch's
 fused_all_gather_matmul, the reference's Triton kernel. Roofline = max(FLOPs / measured cuBLAS
-peak, NVLink bytes in / 770 GB/s)."""
+peak, NVLink bytes in / 770 GB/s). ``--shape M,N,K`` (repeatable list) follows the reference: per
+rank an A shard [M, K] and B [K, N], so the GEMM is [M * world_size, K] x [K, N]; ``-dtype`` is
+accepted and must be bfloat16."""
 from __future__ import annotations
 
 import argparse
@@ -10,7 +12,7 @@ import argparse
 import torch
 import torch.distributed as dist
 
-from common import finish, load_reference, peaks, print_table, setup, try_time, NVLINK_GBS_MEASURED
+from common import check_dtype, shape_triple, finish, load_reference, peaks, print_table, setup, try_time, NVLINK_GBS_MEASURED
 
 
 def main():
@@ -18,9 +20,13 @@ def main():
     ap.add_argument("--M", type=int, nargs="*", default=[2048, 8192])
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--N", type=int, default=28672, help="global N; each rank holds N / world_size columns")
+    ap.add_argument("--shape", type=shape_triple, nargs="+", default=None,
+                    help="per-rank shapes M,N,K as in the reference's script (overrides --M/--N/--K)")
+    ap.add_argument("-dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=15)
     ap.add_argument("--save-path", default="results/bench_all_gather_matmul")
     args = ap.parse_args()
+    check_dtype(args.dtype)
     rank, ws, dev = setup()
     from kraken_b200 import fused
     from kraken_b200.parallel import symm_mem
@@ -29,8 +35,9 @@ def main():
     ref, why = load_reference()
     pk = peaks()
     rows = []
-    for M in args.M:
-        Ml, K, Nl = M // ws, args.K, args.N // ws
+    problems = [(m * ws, k, n) for (m, n, k) in args.shape] if args.shape else [(M, args.K, args.N // ws) for M in args.M]
+    for M, K, Nl in problems:
+        Ml = M // ws
         a = torch.randn(Ml, K, device=dev).to(torch.bfloat16)
         bt = (0.02 * torch.randn(Nl, K, device=dev)).to(torch.bfloat16)
         b = bt.t()

@@ -4,6 +4,10 @@ ops and the reference's Triton kernels. Reports device-timed median microseconds
 and bus bandwidth 2(n-1)/n * S / t.
 
     torchrun --nnodes 1 --nproc-per-node N --master-addr 127.0.0.1 benchmark/benchmark_all_reduce.py
+
+The reference's flags are accepted: ``--size`` (tensor lengths in elements; overrides the byte sweep),
+``-dtype`` (bfloat16 only), ``--backend`` (this script's column names, or the reference's
+nccl / triton_1shot / triton_2shot / dist_multimem / dist_1shot / dist_2shot), ``--save-path``.
 """
 from __future__ import annotations
 
@@ -12,17 +16,27 @@ import argparse
 import torch
 import torch.distributed as dist
 
-from common import bus_bandwidth_gbs, finish, load_reference, print_table, setup, try_time, NVLINK_GBS_MEASURED
+from common import (bus_bandwidth_gbs, check_dtype, finish, load_reference, plot_rows, print_table, setup, try_time,
+                    NVLINK_GBS_MEASURED)
+
+_REF_NAMES = {"triton_1shot": "ref_triton_one_shot", "triton_2shot": "ref_triton_two_shot", "dist_multimem": "torch_multimem",
+              "dist_1shot": "torch_one_shot", "dist_2shot": "torch_two_shot"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-bytes", type=int, default=4096)
     ap.add_argument("--max-bytes", type=int, default=256 << 20)
+    ap.add_argument("--step", type=int, default=2, help="factor between consecutive sizes")
+    ap.add_argument("--size", type=int, nargs="+", default=None, help="tensor lengths in elements (reference flag)")
+    ap.add_argument("-dtype", default="bfloat16")
     ap.add_argument("--backend", nargs="*", default=None)
     ap.add_argument("--iters", type=int, default=25)
     ap.add_argument("--save-path", default="results/bench_all_reduce")
     args = ap.parse_args()
+    check_dtype(args.dtype)
+    if args.backend:
+        args.backend = [_REF_NAMES.get(b, b) for b in args.backend]
     rank, ws, dev = setup()
     from kraken_b200 import comm
     from kraken_b200.parallel import symm_mem
@@ -30,8 +44,14 @@ def main():
 
     ref, why = load_reference()
     rows = []
-    nbytes = args.min_bytes
-    while nbytes <= args.max_bytes:
+    if args.size:
+        sizes = [2 * n for n in args.size]
+    else:
+        sizes, nb_ = [], args.min_bytes
+        while nb_ <= args.max_bytes:
+            sizes.append(nb_)
+            nb_ *= max(2, args.step)
+    for nbytes in sizes:
         numel = nbytes // 2
         x = torch.randn(numel, device=dev).to(torch.bfloat16)
         xs = symm_mem.empty(numel, dtype=torch.bfloat16, device=dev)
@@ -44,6 +64,7 @@ def main():
         dist.all_reduce(golden)
         backends = {
             "one_shot": lambda: comm.one_shot_all_reduce(xs),
+            "one_shot_pull": lambda: comm.one_shot_all_reduce(xs, algo="pull"),
             "two_shot": lambda: comm.two_shot_all_reduce(x),
             "multimem": lambda: comm.multimem_all_reduce(xm),
             "nccl": lambda: dist.all_reduce(x.clone()),
@@ -63,6 +84,7 @@ def main():
             why = why or str(e)
         if nbytes > (32 << 20):
             backends.pop("one_shot", None)          # pull traffic (n-1)*S: pointless at this size
+            backends.pop("one_shot_pull", None)
             backends.pop("torch_one_shot", None)
             backends.pop("ref_triton_one_shot", None)
         # correctness gate before timing, as the reference's benchmark does
@@ -84,9 +106,9 @@ def main():
             row["best_busGBs"] = bus_bandwidth_gbs("all_reduce", nbytes, ws, best)
             row["frac_of_link"] = row["best_busGBs"] / NVLINK_GBS_MEASURED
         rows.append(row)
-        nbytes *= 4
     cols = ["bytes"] + sorted({k for r in rows for k in r if k != "bytes"})
     print_table(rows, cols, f"all_reduce sweep, {ws} x B200 (us = median, max over ranks)", f"{args.save_path}_ws{ws}")
+    plot_rows(rows, ["bytes"], f"{args.save_path}_ws{ws}")
     finish()
 
 

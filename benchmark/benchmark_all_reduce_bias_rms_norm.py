@@ -9,13 +9,13 @@ import argparse
 import torch
 import torch.distributed as dist
 
-from common import finish, load_reference, print_table, setup, try_time
+from common import finish, load_reference, plot_rows, print_table, setup, try_time
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--max-b", type=int, default=512)
-    ap.add_argument("--d-size", type=int, default=5120)
+    ap.add_argument("--max-b", "--max_b", dest="max_b", type=int, default=512)
+    ap.add_argument("--d-size", "--d_size", dest="d_size", type=int, default=5120)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--save-path", default="results/bench_all_reduce_bias_rms_norm")
     args = ap.parse_args()
@@ -60,6 +60,7 @@ def main():
 
         backends = {
             "one_shot_fused": lambda: fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
+            "one_shot_pull_fused": lambda: fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5, algo="pull"),
             "two_shot_fused": lambda: fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
             "ours_unfused": ours_unfused,
             "nccl_unfused": nccl_unfused,
@@ -68,8 +69,9 @@ def main():
             # the reference's one-shot kernel launches one block per row: stay inside its signal pad
             backends["ref_one_shot_fused"] = lambda: ref.fused.one_shot_all_reduce_bias_rms_norm(tpad, x, full_bias, w, y, 1e-5)
             backends["ref_two_shot_fused"] = lambda: ref.fused.two_shot_all_reduce_bias_rms_norm(tpad, x, full_bias, w, y, 1e-5)
-        fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5)
-        torch.testing.assert_close(y.float(), gold, atol=1e-1, rtol=1e-1)
+        for fn in (fused.two_shot_all_reduce_bias_rms_norm, fused.one_shot_all_reduce_bias_rms_norm):
+            fn(pad, x, bias, w, y, 1e-5)
+            torch.testing.assert_close(y.float(), gold, atol=1e-1, rtol=1e-1)
         row = {"b": b, "bytes": b * D * 2}
         for name, fn in backends.items():
             us, err = try_time(fn, iters=args.iters, warmup=20)
@@ -78,6 +80,7 @@ def main():
         b *= 2
     cols = ["b", "bytes"] + sorted({k for r in rows for k in r if k.endswith("_us")})
     print_table(rows, cols, f"all_reduce + bias + rms_norm, d={D}, {ws} x B200", f"{args.save_path}_ws{ws}")
+    plot_rows(rows, ["b"], f"{args.save_path}_ws{ws}")
     finish()
 
 

@@ -1,7 +1,9 @@
 """Matmul + reduce-scatter (reference: benchmark/benchmark_matmul_reduce_scatter.py). Per rank:
 A bf16 [M, K/ws], B bf16 [K/ws, N] (b.T contiguous); output [M/ws, N]. Backends: this library's
 fused kernel and its copy-engine variant, cuBLAS + NCCL reduce_scatter, torch's
-fused_matmul_reduce_scatter, the reference's Triton kernels."""
+fused_matmul_reduce_scatter, the reference's Triton kernels. ``--shape M,N,K`` (repeatable list)
+follows the reference: per rank A [M, K] and B [K, N]; ``-dtype`` is accepted and must be bfloat16
+(the reference's script defaults to float32 inputs, which this library would cast to bf16)."""
 from __future__ import annotations
 
 import argparse
@@ -9,7 +11,7 @@ import argparse
 import torch
 import torch.distributed as dist
 
-from common import finish, load_reference, peaks, print_table, setup, try_time, NVLINK_GBS_MEASURED
+from common import check_dtype, shape_triple, finish, load_reference, peaks, print_table, setup, try_time, NVLINK_GBS_MEASURED
 
 
 def main():
@@ -17,17 +19,21 @@ def main():
     ap.add_argument("--M", type=int, nargs="*", default=[2048, 8192])
     ap.add_argument("--K", type=int, default=28672, help="global K; each rank holds K / world_size")
     ap.add_argument("--N", type=int, default=8192)
+    ap.add_argument("--shape", type=shape_triple, nargs="+", default=None,
+                    help="per-rank shapes M,N,K as in the reference's script (overrides --M/--N/--K)")
+    ap.add_argument("-dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=15)
     ap.add_argument("--save-path", default="results/bench_matmul_reduce_scatter")
     args = ap.parse_args()
+    check_dtype(args.dtype)
     rank, ws, dev = setup()
     from kraken_b200 import fused
 
     ref, why = load_reference()
     pk = peaks()
     rows = []
-    for M in args.M:
-        Kl, N = args.K // ws, args.N
+    problems = [(m, k, n) for (m, n, k) in args.shape] if args.shape else [(M, args.K // ws, args.N) for M in args.M]
+    for M, Kl, N in problems:
         a = torch.randn(M, Kl, device=dev).to(torch.bfloat16)
         bt = (0.02 * torch.randn(N, Kl, device=dev)).to(torch.bfloat16)
         b = bt.t()

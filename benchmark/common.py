@@ -96,6 +96,34 @@ def print_table(rows: list[dict], columns: list[str], title: str, save_prefix: s
             json.dump({"title": title, "rows": rows}, f, indent=1)
 
 
+def shape_triple(text: str) -> tuple[int, int, int]:
+    """"M,N,K" or "MxNxK" -> (M, N, K): the `--shape` argument of the GEMM benchmarks (the reference
+    takes the same three numbers, benchmark/benchmark_all_gather_matmul.py:222-232)."""
+    parts = [t for t in text.replace("x", ",").replace("(", "").replace(")", "").split(",") if t.strip()]
+    if len(parts) != 3:
+        raise ValueError("a shape is three integers: M,N,K")
+    return tuple(int(t) for t in parts)
+
+
+def check_dtype(name: str) -> None:
+    """`-dtype` is accepted for command-line compatibility with the reference's scripts; the
+    tensor-core and collective kernels of this library are bf16 (fp32 inputs would be cast)."""
+    if name not in ("bfloat16", "bf16"):
+        raise SystemExit(f"-dtype {name}: this library's kernels are bfloat16; run with -dtype bfloat16")
+
+
+def plot_rows(rows: list[dict], label_keys: list[str], save_prefix: str | None) -> None:
+    """Line chart of every *_us column over the rows (rank 0), as the reference's bias benchmarks do."""
+    if not save_prefix or (dist.is_initialized() and dist.get_rank() != 0) or not rows:
+        return
+    from kraken_b200._logging import plot_experiment_comparison
+
+    names = sorted({k for r in rows for k in r if k.endswith("_us") and k != "roofline_us"})
+    sizes = [" ".join(f"{k}:{r[k]}" for k in label_keys) for r in rows]
+    data = [[r.get(n) for n in names] for r in rows]
+    plot_experiment_comparison(sizes, [n[:-3] for n in names], data, save_prefix + ".png")
+
+
 def finish():
     if dist.is_initialized():
         dist.barrier(device_ids=[torch.cuda.current_device()])

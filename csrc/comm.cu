@@ -280,6 +280,7 @@ __device__ void all_gather_body(const CommParams& p, unsigned bid, unsigned nb) 
     const int src = (p.rank + step + 1) % p.ws;
     for (int sp = 0; sp < p.splits; ++sp) {
       const int idx = src * p.splits + sp;
+      if (!kr_in_bounds(idx >= 0 && idx < p.ws * p.splits, p.sync, 74)) continue;
       const char* from = symm_buf(p, src) + (size_t)sp * chunk_vec * 16;
       char* to = (char*)p.output + (size_t)idx * chunk_vec * 16;
       size_t v = first;
@@ -350,9 +351,15 @@ __device__ void sync_test_body(const SyncTestParams& p, unsigned bid, unsigned n
       bool ok = wait_gmem_barrier(p.flags + src, 1u, p.sync, 23);
       if (threadIdx.x == 0) p.out[bid] = ok ? ld_volatile_u32(p.out + src) : 0u;
     }
-  } else {
+  } else if (p.mode == 2) {
     bool ok = wait_gmem_barrier(p.flags + bid, 1u, p.sync, 24);
     if (threadIdx.x == 0) p.out[bid] = ok ? 1u : 2u;
+  } else {
+    // Bounds-check self-test: index num_producers is checked against a limit of num_producers
+    // (one past the end). In the debug build the check fails, records KR_ERR_BOUNDS and the store is
+    // skipped (out stays 0); in the regular build the check is compiled away and the store happens —
+    // inside the buffer either way, which the host sizes with one spare word.
+    if (threadIdx.x == 0 && kr_in_bounds(p.num_producers < p.num_producers, p.sync, 75)) p.out[p.num_producers] = 3u;
   }
 }
 KR_DEFINE_RANKED_KERNEL(sync_test, SyncTestParams, 128)
@@ -515,7 +522,8 @@ KR_API int kr_reduce_slabs(const void* slabs, void* out, int ws, int start, unsi
   return KR_SUCCESS;
 }
 
-// mode 0: three symm_mem_sync patterns per block; 1: gmem arrive/wait; 2: wait that must time out.
+// mode 0: three symm_mem_sync patterns per block; 1: gmem arrive/wait; 2: wait that must time out;
+// 3: bounds-check self-test (out needs num_producers + 1 words).
 KR_API int kr_sync_test(uint32_t* const* pads, int rank, int ws, uint32_t* flags, uint32_t* out, int mode,
                         int num_blocks, int num_producers, cudaStream_t stream) {
   DeviceState* d = device_state();

@@ -399,7 +399,8 @@ __device__ __forceinline__ void ag_push_cta(const GemmParams& p, unsigned comm_i
           const size_t off = next_store * kAgPiece;
           const uint32_t bytes = (uint32_t)min((size_t)kAgPiece, chunk_bytes - off);
           fence_proxy_async();
-          bulk_store_1d(to + off, base + slot * kAgPiece, bytes);
+          if (kr_in_bounds(idx < p.ws * p.splits && off + bytes <= chunk_bytes && dst >= 0 && dst < p.ws, p.sync, 72))
+            bulk_store_1d(to + off, base + slot * kAgPiece, bytes);
           bulk_commit_group();
           ++stored;
           next_store += n_comm;

@@ -146,7 +146,9 @@ struct RsPullHooks : HookDefaults {
     epi_bar_sync();   // all four epilogue warps' stores of this tile are complete
     if (q == 0 && lane == 0) {
       const int owner = (tr * kBM) / p.slab_rows;
-      red_add_release_sys(counter(p, owner, tr, tc), 1u);
+      const long long unit = (long long)(tr - owner * (p.slab_rows / kBM)) * p.tiles_c + tc;
+      if (kr_in_bounds(owner >= 0 && owner < p.ws && unit >= 0 && unit < (long long)p.rs_done_off, p.sync, 70))
+        red_add_release_sys(counter(p, owner, tr, tc), 1u);
     }
     return true;
   }
@@ -209,6 +211,9 @@ struct RsPullHooks : HookDefaults {
     const int lrow0 = tr * kBM - p.rank * p.slab_rows + sub * p.rs_sub_rows;
     const int rows = min(p.rs_sub_rows, p.slab_rows - lrow0);
     const int total = rows * vpr;
+    if (!kr_in_bounds(lrow0 >= 0 && rows > 0 && lrow0 + rows <= p.slab_rows && col0 >= 0 && col0 + vpr * 8 <= N &&
+                          (f - (p.pads[p.rank] + p.flag_base)) < (long long)p.rs_done_off, p.sync, 71))
+      return false;
     if (p.mc_ptr != nullptr) {
       // in-switch sum (pull only)
       const char* src = (const char*)p.mc_ptr + p.stage_off + (size_t)p.rank * slab_bytes(p) + ((size_t)lrow0 * N + col0) * 2;

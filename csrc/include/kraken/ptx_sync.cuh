@@ -59,6 +59,19 @@ __device__ __forceinline__ void set_status(const SyncCtx& c, uint32_t word) {
   atomicCAS(c.status, 0u, word);
 }
 
+// ---- debug bounds checks -----------------------------------------------------------------------
+// Compiled in with -DKRAKEN_DEBUG=1 (the library's debug build), compiled away otherwise. A failed
+// check records KR_ERR_BOUNDS with its site in the status word and returns false; the caller then
+// SKIPS the access, so a wrong index shows up as a host-side error, never as a memory fault.
+#ifdef KRAKEN_DEBUG
+__device__ __forceinline__ bool kr_in_bounds(bool ok, const SyncCtx& c, uint32_t site) {
+  if (!ok) set_status(c, make_status(KR_ERR_BOUNDS, site, 0, blockIdx.x));
+  return ok;
+}
+#else
+__device__ __forceinline__ constexpr bool kr_in_bounds(bool, const SyncCtx&, uint32_t) { return true; }
+#endif
+
 // ---- raw memory-model operations -------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {

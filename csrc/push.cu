@@ -44,6 +44,7 @@ __device__ __forceinline__ char* slot_of(const PushParams& p, int dst, int src) 
 
 // Writes one 16-byte vector of this rank's data into slot [rank] of every peer.
 __device__ __forceinline__ void push_vec(const PushParams& p, size_t byte_off, const U4& x) {
+  if (!kr_in_bounds(byte_off + 16 <= p.slot_bytes, p.sync, 73)) return;
   if (p.mc_ptr != nullptr) {
     multimem_st16((char*)p.mc_ptr + p.half_off + (size_t)p.rank * p.slot_bytes + byte_off, x);
   } else {

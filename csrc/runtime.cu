@@ -113,6 +113,15 @@ using namespace kraken;
 
 KR_API const char* kr_last_error() { return g_last_error.c_str(); }
 
+// 1 when the library was compiled with the device-side bounds checks (-DKRAKEN_DEBUG=1).
+KR_API int kr_is_debug_build() {
+#ifdef KRAKEN_DEBUG
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 KR_API int kr_num_sms() {
   DeviceState* d = device_state();
   return d ? d->num_sms : -1;

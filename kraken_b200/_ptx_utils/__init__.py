@@ -79,5 +79,25 @@ def wait_timeout_test(num_blocks: int = 4) -> torch.Tensor:
     return out
 
 
-__all__ = ["symm_mem_sync", "send_signal", "get_flat_tid", "arrive_gmem_barrier", "wait_gmem_barrier",
+def bounds_check_selftest() -> tuple[int, bool]:
+    """Runs a kernel whose one store is guarded by a bounds check that must fail. Returns
+    (value stored, whether a bounds error was recorded). With the debug build (KRAKEN_DEBUG=1) the
+    store is skipped and the status word carries the bounds code; the regular build compiles the
+    check away. The status word is cleared again."""
+    import ctypes
+
+    L = _lib.lib()
+    out = torch.zeros(8, dtype=torch.int32, device="cuda")
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    pads = torch.zeros(1, dtype=torch.int64, device="cuda")
+    stream = _lib.current_stream_ptr()
+    _lib.check(L.kr_sync_test(pads.data_ptr(), 0, 1, flags.data_ptr(), out.data_ptr(), 3, 1, 4, stream))
+    word = ctypes.c_uint32(0)
+    _lib.check(L.kr_read_status(stream, ctypes.byref(word)))
+    _lib.check(L.kr_clear_status(stream))
+    torch.cuda.synchronize()
+    return int(out[4].item()), (word.value & 0xFF) == 4
+
+
+__all__ = ["symm_mem_sync", "bounds_check_selftest", "send_signal", "get_flat_tid", "arrive_gmem_barrier", "wait_gmem_barrier",
            "gmem_barrier_test", "wait_timeout_test", "HEADER"]

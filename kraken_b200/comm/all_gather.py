@@ -15,6 +15,7 @@ import ctypes
 import torch
 
 from .. import _reference as ref
+from .._logging import utils as _log
 from ..ops import lib as _lib
 from ..parallel import symm_mem
 
@@ -99,6 +100,7 @@ def all_gather_w_progress(a_shared: torch.Tensor, a_out: torch.Tensor | None = N
     else:
         progress.zero_()
     backend = kwargs.get("backend", "ce" if hdl.group.emu is None else "sm")
+    _log.log_kernel_choice("all_gather_w_progress", f"numel={a_shared.numel()} ws={hdl.world_size} splits={splits} engine={backend}")
     if backend == "sm":
         _sm_all_gather_w_progress(a_out, a_shared, progress, splits, int(kwargs.get("max_num_blocks", 0) or 0))
     else:

@@ -171,6 +171,7 @@ def reduce_scatter(tensor: torch.Tensor, **kwargs) -> torch.Tensor:
     else:
         hdl = symm_mem.get_symm_mem_workspace(group, tensor.numel() * 2, tensor.device)
         off, inp = 0, tensor.data_ptr()
+    _dump(f"reduce_scatter numel={tensor.numel()} ws={ws} staged={inp is not None}")
     _lib.check(_lib.lib().kr_reduce_scatter(
         hdl.buffer_ptrs_dev, off, hdl.signal_pad_ptrs_dev, hdl.rank, ws, inp, out.data_ptr(), tensor.numel(),
         _max_blocks(kwargs), 0, _lib.current_stream_ptr()))

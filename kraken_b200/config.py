@@ -20,6 +20,8 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_ONE_SHOT``         ``push`` (default: small one-shot all-reduces write into the peers' workspace and meet in
                             one barrier) or ``pull`` (copy-in, barrier, remote loads, exit barrier)
 ``KRAKEN_RS_NVLS``          ``1``: the pull reduce-scatter sums with ``multimem.ld_reduce`` (default 0: peer loads)
+``KRAKEN_DEBUG``            ``1`` loads the debug build of the native library (device-side bounds checks that record
+                            an error code and skip the access; built on first use)
 ``KRAKEN_NVTX``             ``1`` wraps every public op in an NVTX range named after it (for timeline tools)
 ``KRAKEN_DUMP_KERNEL``      ``1`` prints the kernel variant / tiling each op picks (rank 0)
 ``KRAKEN_SYMM_BACKEND``     ``native`` (default) or ``torch`` (torch.distributed._symmetric_memory)

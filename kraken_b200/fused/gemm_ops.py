@@ -236,6 +236,8 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     hdl._gemm_ar_calls = calls + 1
     algo = {"one_shot": 0, "two_shot": 1}.get(str(kwargs.get("algo", config.force_algo() or "")), -1)
     mc = hdl.multicast_ptr or None
+    _log.log_kernel_choice("gemm_one_shot_all_reduce", f"M={M} N={N} K={K} ws={hdl.world_size} "
+                           f"exchange={('by size', 'one_shot', 'two_shot')[algo + 1]} nvls={bool(mc)}")
     _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, mc, hdl.rank, hdl.world_size,
                                  a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
                                  int(kwargs.get("swap_ab", -1)), algo, calls & 1, config.TILE_FLAG_BASE,
@@ -336,6 +338,7 @@ def gemm_reduce_scatter_ce_persistent(a: torch.Tensor, b: torch.Tensor, reduce_o
                                   _lib.current_stream_ptr()))
         return out
     gemm_out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    _log.log_kernel_choice("gemm_reduce_scatter_ce_persistent", f"M={M} N={N} K={K} ws={ws}: producer GEMM + copy engines + slab reduction")
     hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, dev)
     backend = symm_mem._get_backend_stream(priority=-1)
     cur = torch.cuda.current_stream()

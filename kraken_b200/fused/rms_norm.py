@@ -4,6 +4,7 @@ from __future__ import annotations
 import torch
 
 from .. import _reference as ref
+from .._logging import utils as _log
 from ..ops import lib as _lib
 
 
@@ -16,6 +17,7 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tenso
     if w.numel() != D or D % 8:
         raise ValueError("weight must have the last dimension's size, which must be a multiple of 8")
     xc = x.contiguous()
+    _log.log_kernel_choice("rms_norm", f"rows={xc.numel() // D} D={D}")
     y = torch.empty_like(xc)
     _lib.check(_lib.lib().kr_rms_norm(xc.data_ptr(), w.contiguous().data_ptr(), y.data_ptr(), xc.numel() // D, D,
                                       float(eps), _lib.current_stream_ptr()))

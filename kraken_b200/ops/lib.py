@@ -30,6 +30,7 @@ _P = c_void_p
 _PROTOS = {
     "kr_last_error": (c_char_p, []),
     "kr_num_sms": (c_int, []),
+    "kr_is_debug_build": (c_int, []),
     "kr_set_timeout_ms": (c_int, [c_double]),
     "kr_get_timeout_ms": (c_double, []),
     "kr_status_ptr": (_P, []),
@@ -109,8 +110,12 @@ _PROTOS = {
 }
 
 
+def debug_build_selected() -> bool:
+    return os.environ.get("KRAKEN_DEBUG", "0") == "1"
+
+
 def lib_path() -> str:
-    return str(_build.LIB_PATH)
+    return str(_build.lib_path(debug_build_selected()))
 
 
 def lib() -> ctypes.CDLL:
@@ -120,13 +125,15 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        if os.environ.get("KRAKEN_NO_BUILD", "0") != "1" and _build.is_stale():
+        debug = debug_build_selected()
+        target = _build.lib_path(debug)
+        if os.environ.get("KRAKEN_NO_BUILD", "0") != "1" and _build.is_stale(debug):
             try:
-                _build.build()
+                _build.build(debug=debug)
             except Exception:
-                if not _build.LIB_PATH.exists():
+                if not target.exists():
                     raise
-        handle = ctypes.CDLL(str(_build.LIB_PATH), mode=ctypes.RTLD_GLOBAL)
+        handle = ctypes.CDLL(str(target), mode=ctypes.RTLD_GLOBAL)
         for name, (res, args) in _PROTOS.items():
             fn = getattr(handle, name)
             fn.restype = res
