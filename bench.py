@@ -132,6 +132,9 @@ def run_ours(args):
     def op_rs():
         fused.gemm_reduce_scatter(h_fixed, w_down_t.t())
 
+    def op_rs_ce():
+        fused.gemm_reduce_scatter_ce_persistent(h_fixed, w_down_t.t())
+
     sampler = ClockSampler(gpu_index=dev.index).start() if rank == 0 else None
     for _ in range(max(3, args.warmup)):
         step()
@@ -154,7 +157,8 @@ def run_ours(args):
     ms_step = maxr(sum(times) / len(times))
     # per-op numbers (median, max over ranks)
     ops = {}
-    for name, fn in (("all_gather_matmul", op_ag), ("gemm_reduce_scatter", op_rs)):
+    for name, fn in (("all_gather_matmul", op_ag), ("gemm_reduce_scatter", op_rs),
+                     ("gemm_reduce_scatter_ce_persistent", op_rs_ce)):
         for _ in range(3):
             fn()
         ts = sorted(_event_times(fn, max(3, args.steps), sync))
@@ -171,7 +175,8 @@ def run_ours(args):
     e2e_value = flops_step / (ms_e2e * 1e-3) / 1e12
     per_gemm_flops_rank = 2.0 * M * F * H / ws
     link = 770e9
-    for name, nv_bytes in (("all_gather_matmul", (ws - 1) * Ml * H * 2), ("gemm_reduce_scatter", (ws - 1) * Ml * H * 2)):
+    for name, nv_bytes in (("all_gather_matmul", (ws - 1) * Ml * H * 2), ("gemm_reduce_scatter", (ws - 1) * Ml * H * 2),
+                           ("gemm_reduce_scatter_ce_persistent", (ws - 1) * Ml * H * 2)):
         t_mma = per_gemm_flops_rank / (peaks["bf16_tflops"] * 1e12)
         t_link = nv_bytes / link
         roof = max(t_mma, t_link)

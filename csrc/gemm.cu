@@ -17,23 +17,13 @@
 #include <mutex>
 #include <tuple>
 #include "kraken/gemm_host.h"
+#include "kraken/gemm_hooks.cuh"
 
 namespace kraken {
 
 // ---------------------------------------------------------------------------------------------
 // hooks
 // ---------------------------------------------------------------------------------------------
-struct PlainHooks : HookDefaults {
-  int bn;
-  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
-  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
-  __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
-  __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols, p.use_tma_store ? &p.tmap_out[0] : nullptr};
-  }
-  __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
-};
-
 struct AgHooks : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
@@ -64,189 +54,6 @@ struct AgHooks : HookDefaults {
     return TileDest{(char*)p.out, p.ldo, tr * kBM, tc * bn, p.out_rows, p.out_cols, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
-};
-
-// GEMM -> all-reduce (decode). Two exchange algorithms behind the same main loop:
-//  * one-shot (small M): the fp32 partial tile goes to the rank's OWN staging, a flag goes to
-//    every peer, and every rank sums the tile from all ranks (in-switch with multimem.ld_reduce
-//    when the staging buffer has a multicast mapping, else ws peer loads in rank order).
-//  * two-shot (larger M): tile t belongs to rank t % ws. Every rank stores its partial tile into
-//    the OWNER's staging slot [src]; the owner sums the ws slots from its own memory (rank order,
-//    so every rank receives identical bits), writes the result into every rank's result buffer
-//    (one multimem.st, or ws-1 peer stores) and raises "published" flags; the others copy the tile
-//    out. NVLink bytes per rank drop from (ws-1)·M·N·4 to about 2·(ws-1)/ws·M·N·4.
-// The staging buffer is dedicated to this op. One-shot alternates between two staging halves and
-// two flag banks from call to call, and in two-shot nobody leaves before every tile it takes part
-// in is published, so neither needs an exit barrier.
-struct ArHooks : HookDefaults {
-  int bn;
-  __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
-  __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
-  __device__ __forceinline__ bool before_load(const GemmParams&, int, const CUtensorMap*&, int&) { return true; }
-  __device__ __forceinline__ int tile_of(const GemmParams& p, int tr, int tc) const { return tr * p.tiles_c + tc; }
-  __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
-    char* base;
-    if (p.ar_algo == 0) {
-      base = (char*)p.bufs[p.rank] + p.stage_off;
-    } else {
-      const int owner = tile_of(p, tr, tc) % p.ws;
-      base = (char*)p.bufs[owner] + p.part_off + (size_t)p.rank * p.out_rows * p.out_cols * 4;
-    }
-    return TileDest{base, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
-  }
-  // region of tile (tr, tc) in the orientation of `out`
-  __device__ __forceinline__ void region(const GemmParams& p, int tr, int tc, int& r_lo, int& r_n, int& c_lo, int& c_n) {
-    if (p.transposed) { r_lo = tc * bn; r_n = bn; c_lo = tr * kBM; c_n = kBM; }
-    else { r_lo = tr * kBM; r_n = kBM; c_lo = tc * bn; c_n = bn; }
-  }
-  __device__ __forceinline__ bool wait_count(uint32_t* f, uint32_t need, const GemmParams& p, uint32_t site) {
-    if (need == 0) return true;
-    if (spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, site, 0, blockIdx.x))) {
-      red_add_relaxed_sys(f, 0u - need);
-      return true;
-    }
-    return false;
-  }
-  __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
-    const int tile = tile_of(p, tr, tc);
-    const int tid = q * 32 + lane;   // 0..127 over the epilogue warps
-    int r_lo, r_n, c_lo, c_n;
-    region(p, tr, tc, r_lo, r_n, c_lo, c_n);
-    const int upr = c_n / 4;         // 16-byte units per tile row
-    const bool vec = (p.out_cols % 4) == 0 && (p.ldo % 4) == 0;
-    const size_t mn4 = (size_t)p.out_rows * p.out_cols * 4;
-    epi_bar_sync();                  // the whole tile has been stored
-    if (p.ar_algo == 0) {
-      // ---------------- one-shot ----------------
-      if (tid < p.ws && tid != p.rank) red_add_release_sys(p.pads[tid] + p.flag_base + tile, 1u);
-      if (tid == 0) wait_count(p.pads[p.rank] + p.flag_base + tile, (uint32_t)(p.ws - 1), p, 51);
-      epi_bar_sync();
-      if (!status_ok(p.sync)) return false;
-      for (int i0 = tid; i0 < r_n * upr; i0 += 256) {
-        size_t off[2];
-        int rr[2], cc[2];
-        bool act[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int i = i0 + 128 * k;
-          rr[k] = r_lo + i / upr;
-          cc[k] = c_lo + (i % upr) * 4;
-          act[k] = i < r_n * upr && rr[k] < p.out_rows && cc[k] < p.out_cols;
-          off[k] = ((size_t)rr[k] * p.out_cols + cc[k]) * 4;
-        }
-        if (vec && p.mc_ptr != nullptr) {
-          float4 a[2];
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-            if (act[k]) a[k] = multimem_ld_reduce_f32x4((const char*)p.mc_ptr + p.stage_off + off[k]);
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-            if (act[k]) *(float4*)((float*)p.out + (size_t)rr[k] * p.ldo + cc[k]) = a[k];
-        } else if (vec) {
-          U4 x[2][8];
-          float4 a[2];
-          a[0] = a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s0 = 0; s0 < p.ws; s0 += 8) {
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-#pragma unroll
-              for (int s = 0; s < 8; ++s)
-                if (act[k] && s0 + s < p.ws) x[k][s] = ld16((const char*)p.bufs[s0 + s] + p.stage_off + off[k]);
-#pragma unroll
-            for (int k = 0; k < 2; ++k)
-#pragma unroll
-              for (int s = 0; s < 8; ++s)
-                if (act[k] && s0 + s < p.ws) {
-                  a[k].x += __uint_as_float(x[k][s].x); a[k].y += __uint_as_float(x[k][s].y);
-                  a[k].z += __uint_as_float(x[k][s].z); a[k].w += __uint_as_float(x[k][s].w);
-                }
-          }
-#pragma unroll
-          for (int k = 0; k < 2; ++k)
-            if (act[k]) *(float4*)((float*)p.out + (size_t)rr[k] * p.ldo + cc[k]) = a[k];
-        } else {
-          for (int k = 0; k < 2; ++k) {
-            if (!act[k]) continue;
-            for (int e = 0; e < 4 && cc[k] + e < p.out_cols; ++e) {
-              float acc = 0.f;
-              for (int s = 0; s < p.ws; ++s)
-                acc += ((const volatile float*)((const char*)p.bufs[s] + p.stage_off + off[k]))[e];
-              ((float*)p.out)[(size_t)rr[k] * p.ldo + cc[k] + e] = acc;
-            }
-          }
-        }
-      }
-      return true;
-    }
-    // ---------------- two-shot ----------------
-    const int owner = tile % p.ws;
-    if (tid == 0) red_add_release_sys(p.pads[owner] + p.flag_base + tile, 1u);
-    if (owner == p.rank) {
-      if (tid == 0) wait_count(p.pads[p.rank] + p.flag_base + tile, (uint32_t)p.ws, p, 58);
-      epi_bar_sync();
-      if (!status_ok(p.sync)) return false;
-      const char* part = (const char*)p.bufs[p.rank] + p.part_off;
-      for (int i = tid; i < r_n * upr; i += 128) {
-        const int rr = r_lo + i / upr, cc = c_lo + (i % upr) * 4;
-        if (rr >= p.out_rows || cc >= p.out_cols) continue;
-        const size_t off = ((size_t)rr * p.out_cols + cc) * 4;
-        if (vec) {
-          U4 x[8];
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s0 = 0; s0 < p.ws; s0 += 8) {
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (s0 + s < p.ws) x[s] = ld16(part + (size_t)(s0 + s) * mn4 + off);
-#pragma unroll
-            for (int s = 0; s < 8; ++s)
-              if (s0 + s < p.ws) {
-                a.x += __uint_as_float(x[s].x); a.y += __uint_as_float(x[s].y);
-                a.z += __uint_as_float(x[s].z); a.w += __uint_as_float(x[s].w);
-              }
-          }
-          *(float4*)((float*)p.out + (size_t)rr * p.ldo + cc) = a;
-          const U4 v = U4{__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w)};
-          if (p.mc_ptr != nullptr) {
-            multimem_st16((char*)p.mc_ptr + p.res_off + off, v);
-          } else {
-            for (int s = 1; s < p.ws; ++s) {
-              int peer = p.rank + s;
-              if (peer >= p.ws) peer -= p.ws;
-              st16((char*)p.bufs[peer] + p.res_off + off, v);
-            }
-          }
-        } else {
-          for (int e = 0; e < 4 && cc + e < p.out_cols; ++e) {
-            float acc = 0.f;
-            for (int s = 0; s < p.ws; ++s) acc += ((const float*)(part + (size_t)s * mn4 + off))[e];
-            ((float*)p.out)[(size_t)rr * p.ldo + cc + e] = acc;
-            for (int s = 1; s < p.ws; ++s)
-              ((float*)((char*)p.bufs[(p.rank + s) % p.ws] + p.res_off + off))[e] = acc;
-          }
-        }
-      }
-      epi_bar_sync();                // every thread's result stores are issued
-      if (tid < p.ws && tid != p.rank) red_add_release_sys(p.pads[tid] + p.flag2_base + tile, 1u);
-      return true;
-    }
-    if (tid == 0) wait_count(p.pads[p.rank] + p.flag2_base + tile, 1u, p, 59);
-    epi_bar_sync();
-    if (!status_ok(p.sync)) return false;
-    const char* res = (const char*)p.bufs[p.rank] + p.res_off;
-    for (int i = tid; i < r_n * upr; i += 128) {
-      const int rr = r_lo + i / upr, cc = c_lo + (i % upr) * 4;
-      if (rr >= p.out_rows || cc >= p.out_cols) continue;
-      const size_t off = ((size_t)rr * p.out_cols + cc) * 4;
-      if (vec) {
-        const U4 v = ld16(res + off);
-        st16((char*)((float*)p.out + (size_t)rr * p.ldo + cc), v);
-      } else {
-        for (int e = 0; e < 4 && cc + e < p.out_cols; ++e)
-          ((float*)p.out)[(size_t)rr * p.ldo + cc + e] = ((const float*)(res + off))[e];
-      }
-    }
-    return true;
-  }
 };
 
 // Producer GEMM of the copy-engine reduce-scatter variant
@@ -530,19 +337,21 @@ struct TmapKey {
   const void* ptr;
   unsigned long long rows, cols, ld;
   unsigned box_rows;
+  int elt;
   bool operator<(const TmapKey& o) const {
-    return std::tie(ptr, rows, cols, ld, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows);
+    return std::tie(ptr, rows, cols, ld, box_rows, elt) < std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows, o.elt);
   }
 };
 static std::mutex g_tmap_mu;
 static std::map<TmapKey, CUtensorMap> g_tmap_cache;
 static unsigned long long g_tmap_hits = 0, g_tmap_misses = 0;
 
-// Tensor map of a row-major bf16 matrix [rows, cols] (cols contiguous, `ld` elements per row),
-// box = 64 columns x box_rows rows, 128-byte swizzle, out-of-range elements read as zero.
+// Tensor map of a row-major matrix [rows, cols] of bf16 (elt 2) or fp32 (elt 4) elements (cols
+// contiguous, `ld` elements per row), box = 128 bytes of columns x box_rows rows, 128-byte swizzle,
+// out-of-range elements read as zero.
 int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
-                    unsigned box_rows, CUtensorMap* out) {
-  TmapKey key{ptr, rows, cols, ld, box_rows};
+                    unsigned box_rows, CUtensorMap* out, int elt) {
+  TmapKey key{ptr, rows, cols, ld, box_rows, elt};
   {
     std::lock_guard<std::mutex> lk(g_tmap_mu);
     auto it = g_tmap_cache.find(key);
@@ -553,14 +362,16 @@ int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, 
     }
   }
   KR_REQUIRE(((uintptr_t)ptr & 15) == 0, "GEMM operand must be 16-byte aligned");
-  KR_REQUIRE((ld * 2) % 16 == 0, "GEMM operand row stride must be a multiple of 8 elements");
+  KR_REQUIRE(elt == 2 || elt == 4, "GEMM operands are bf16 or fp32");
+  KR_REQUIRE((ld * elt) % 16 == 0, "GEMM operand row stride must be a multiple of 16 bytes");
   KR_REQUIRE(box_rows >= 1 && box_rows <= 256, "bad TMA box");
   cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstride[1] = {ld * 2};
-  cuuint32_t box[2] = {64, box_rows};
+  cuuint64_t gstride[1] = {ld * (unsigned long long)elt};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elt), box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
-  KR_CU(cuTensorMapEncodeTiled, &m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box,
+  KR_CU(cuTensorMapEncodeTiled, &m, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+        const_cast<void*>(ptr), gdim, gstride, box,
         estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   {
@@ -610,6 +421,9 @@ static int pick_bn(int rows_c) {
   return 16;
 }
 
+// The tf32 kernels exist for three column-tile widths.
+static int tf32_bn(int rows_c) { return rows_c <= 16 ? 16 : (rows_c <= 64 ? 64 : 256); }
+
 constexpr size_t kAgSmem = (size_t)kAgSlots * kAgPiece + 1024 + 128;
 static_assert(kAgSmem <= (size_t)kSmemLimit, "comm ring exceeds shared memory");
 
@@ -627,7 +441,7 @@ bool pair_enabled() {
 // ranks, and no rank emulation (the emulated launch is cooperative, not clustered).
 static bool pair_eligible(int bn, const GemmParams& p) {
   if (!pair_enabled() || emu_recorder().active) return false;
-  if (bn != 256 || p.transposed || p.rows_r < 256) return false;
+  if (bn != 256 || p.transposed || p.rows_r < 256 || p.in_fp32) return false;
   if (p.mode == GEMM_AR) return false;
   if (p.mode == GEMM_CE && (p.slab_rows % 256) != 0) return false;
   return true;
@@ -665,6 +479,7 @@ static int launch_pair(GemmParams p, unsigned cap, unsigned n_comm, cudaStream_t
 }
 
 static int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream) {
+  if (p.in_fp32) return launch_gemm_tf32(bn, p, nb, stream);
   const size_t floor_smem = p.mode == GEMM_AG ? kAgSmem : 0;   // comm CTAs reuse the block's shared memory
   auto sm = [&](size_t s) { return s > floor_smem ? s : floor_smem; };
   switch (bn) {
@@ -688,8 +503,9 @@ unsigned grid_cap(const DeviceState* d) {
 // Fills the operand/tiling part of the parameter block for C[M,N] = A[M,K] * Bt[N,K]^T.
 // swap: the weights (Bt) become the 128-row operand and the tile is stored transposed.
 int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, long long ldb, int M, int N,
-                         int K, bool swap, int bn_override, int* bn_out) {
-  KR_REQUIRE(M >= 1 && N >= 1 && K >= 8 && K % 8 == 0, "GEMM needs K % 8 == 0 and positive sizes");
+                         int K, bool swap, int bn_override, int* bn_out, int elt) {
+  KR_REQUIRE(M >= 1 && N >= 1 && K >= 8 && (K * elt) % 16 == 0, "GEMM needs K rows of whole 16-byte units and positive sizes");
+  p.in_fp32 = elt == 4 ? 1 : 0;
   const void* r = swap ? bt : a;
   const void* c = swap ? a : bt;
   long long ldr = swap ? ldb : lda, ldc = swap ? lda : ldb;
@@ -703,9 +519,9 @@ int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, l
   p.group_r = default_group_r();
   p.pivot_r = 0;
   p.transposed = swap ? 1 : 0;
-  int rc = get_tmap(r, p.rows_r, K, ldr, kBM, &p.tmap_r);
+  int rc = get_tmap(r, p.rows_r, K, ldr, kBM, &p.tmap_r, elt);
   if (rc) return rc;
-  rc = get_tmap(c, p.rows_c, K, ldc, bn, &p.tmap_c);
+  rc = get_tmap(c, p.rows_c, K, ldc, bn, &p.tmap_c, elt);
   if (rc) return rc;
   p.host_c_ptr = c;
   p.host_ldc = ldc;
@@ -727,17 +543,20 @@ KR_API int kr_tmap_cache_stats(unsigned long long* hits, unsigned long long* mis
 // out[M,N] (bf16 or fp32, row stride ldo) = a[M,K] (row stride lda) * bt[N,K]^T (row stride ldb).
 // swap_ab: -1 auto (weights on the 128-row side when M <= 64), 0/1 forced.
 // use_pair: 0 forces the single-CTA kernel, anything else lets eligible shapes use CTA pairs.
+// in_fp32: a and bt hold fp32 and are multiplied as tf32 (single-CTA kernels; strides in elements).
 KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long ldb, void* out, long long ldo, int M,
                         int N, int K, int out_fp32, int swap_ab, int bn_override, int max_ctas, int use_pair,
-                        cudaStream_t stream) {
+                        int in_fp32, cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const bool swap = swap_ab < 0 ? (M <= 64 && N >= 128) : swap_ab != 0;
   int bn = 0;
-  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, swap, bn_override, &bn);
+  if (in_fp32 && bn_override <= 0) bn_override = tf32_bn(swap ? M : N);
+  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, swap, bn_override, &bn, in_fp32 ? 4 : 2);
   if (rc) return rc;
+  if (in_fp32) KR_REQUIRE(bn == 16 || bn == 64 || bn == 256, "tf32 GEMM supports column tiles of 16, 64 and 256");
   p.mode = GEMM_PLAIN;
   p.out = out;
   p.ldo = ldo;
@@ -841,7 +660,7 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
 KR_API int kr_gemm_ar_bf16(void* const* bufs, uint32_t* const* pads, void* mc_ptr, int rank, int ws, const void* a,
                            long long lda, const void* bt, long long ldb, void* out, long long ldo, int M, int N, int K,
                            int swap_ab, int algo, int call_parity, uint32_t flag_base, unsigned long long pad_words,
-                           unsigned long long staging_bytes, cudaStream_t stream) {
+                           unsigned long long staging_bytes, int in_fp32, cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
@@ -855,8 +674,9 @@ KR_API int kr_gemm_ar_bf16(void* const* bufs, uint32_t* const* pads, void* mc_pt
   while (bn_pick > 16 && tiles_r * ((rows_c + bn_pick - 1) / bn_pick) < d->num_sms / 2 &&
          tiles_r * ((rows_c + bn_pick / 2 - 1) / (bn_pick / 2)) <= d->num_sms)
     bn_pick /= 2;
+  if (in_fp32) bn_pick = bn_pick <= 16 ? 16 : (bn_pick <= 64 ? 64 : 256);
   int bn = 0;
-  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, swap, bn_pick, &bn);
+  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, swap, bn_pick, &bn, in_fp32 ? 4 : 2);
   if (rc) return rc;
   p.mode = GEMM_AR;
   p.out = out;

@@ -58,6 +58,7 @@ struct alignas(64) GemmParams {
   int mode;
   int transposed;            // 1: D tile is C^T (store element (i,j) at out[j][i])
   int out_fp32;              // 1: fp32 output, 0: bf16
+  int in_fp32;               // 1: fp32 operands multiplied as tf32 (single-CTA kernels), 0: bf16
   int num_mma_ctas;          // CTAs [0, num_mma_ctas) run the GEMM; the rest are comm CTAs (AG)
   // output (PLAIN / AG / final result of RS and AR)
   // TMA-store destinations (bf16 row-major): [0] = `out`; GEMM->RS: [o] = rank o's staging slot for
@@ -337,10 +338,13 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
   return true;
 }
 
-template <int BN, class Hooks>
+// ELT = bytes per operand element: 2 (bf16, kind::f16) or 4 (fp32 read as tf32, kind::tf32). A stage
+// always holds 128-byte rows (64 bf16 or 32 fp32 along K) and feeds four MMAs of 32 bytes of K each.
+template <int BN, class Hooks, int ELT = 2>
 __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid, unsigned nb, Hooks& hooks,
                                               unsigned char* smem_raw) {
   using Cfg = GemmCfg<BN>;
+  constexpr int kStageK = 128 / ELT;            // operand elements along K per stage
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // ---- shared memory carve-up (1024-byte aligned for the 128-byte swizzle)
@@ -376,7 +380,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
   const uint32_t tmem_base = *tmem_slot;
 
   const int total_tiles = p.tiles_r * p.tiles_c;
-  const int num_kb = (p.K + kBK - 1) / kBK;
+  const int num_kb = (p.K + kStageK - 1) / kStageK;
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -397,8 +401,8 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
           if (!ok) break;
           mbar_expect_tx(full_bar(s), Cfg::A_BYTES + Cfg::B_BYTES);
           const uint32_t sa = stage0 + s * Cfg::STAGE;
-          tma_load_2d(sa, rmap, full_bar(s), kb * kBK, row0);
-          tma_load_2d(sa + Cfg::A_BYTES, &p.tmap_c, full_bar(s), kb * kBK, tc * BN);
+          tma_load_2d(sa, rmap, full_bar(s), kb * kStageK, row0);
+          tma_load_2d(sa + Cfg::A_BYTES, &p.tmap_c, full_bar(s), kb * kStageK, tc * BN);
           if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -406,7 +410,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
   } else if (warp == 1) {
     // ================= MMA issuer =================
     if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN);
+      constexpr uint32_t idesc = ELT == 2 ? make_idesc_bf16(kBM, BN) : make_idesc_tf32(kBM, BN);
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
@@ -428,8 +432,10 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
           const uint64_t adesc = make_smem_desc_sw128(sa);
           const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            if (ELT == 2) umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           umma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
           if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
         }

@@ -32,16 +32,37 @@ struct NormParams {
 __device__ __forceinline__ char* symm_buf(const NormParams& p, int r) { return (char*)p.bufs[r] + p.buf_off; }
 
 // ---- standalone RMSNorm ----------------------------------------------------------------------
+// A block walks rows r, r + gridDim.x, ...; the NEXT row's vectors are requested before the current
+// row is reduced and stored, so every block always has a row of loads in flight (the reduction's
+// two block barriers would otherwise leave the memory pipe idle once per row).
 __global__ void __launch_bounds__(kNormMaxThreads) rms_norm_kernel(const __grid_constant__ NormParams p) {
   __shared__ float smem[32];
   const int nvec = p.D / 8;
-  for (int r = blockIdx.x; r < p.rows; r += gridDim.x) {
+  U4 nx[kNormVpt];
+  int r = blockIdx.x;
+  if (r < p.rows) {
     const char* xrow = (const char*)p.x + (size_t)r * p.D * 2;
+#pragma unroll
+    for (int i = 0; i < kNormVpt; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) nx[i] = ld16(xrow + (size_t)v * 16);
+    }
+  }
+  for (; r < p.rows; r += gridDim.x) {
     float f[kNormVpt][8];
 #pragma unroll
     for (int i = 0; i < kNormVpt; ++i) {
-      int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) unpack8(ld16(xrow + (size_t)v * 16), f[i]);
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) unpack8(nx[i], f[i]);
+    }
+    const int rn = r + gridDim.x;
+    if (rn < p.rows) {
+      const char* xrow = (const char*)p.x + (size_t)rn * p.D * 2;
+#pragma unroll
+      for (int i = 0; i < kNormVpt; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) nx[i] = ld16(xrow + (size_t)v * 16);
+      }
     }
     rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + (size_t)r * p.D * 2, smem);
   }
@@ -221,7 +242,10 @@ KR_API int kr_rms_norm(const void* x, const void* w, void* y, int rows, int D, f
   memset(&p, 0, sizeof(p));
   p.x = x; p.y = y; p.w = w; p.rows = rows; p.D = D; p.eps = eps;
   const unsigned nt = norm_threads(D, rows >= 2 * d->num_sms ? kNormVpt : 1);
-  const unsigned resident = 2048 / nt > 0 ? 2048 / nt : 1;
+  // one wave of co-resident blocks (the register file, not the thread count, is what limits it)
+  int per_sm = 0;
+  KR_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, rms_norm_kernel, (int)nt, 0));
+  const unsigned resident = per_sm > 0 ? (unsigned)per_sm : 1u;
   const unsigned cap = (unsigned)d->num_sms * resident;
   unsigned nb = (unsigned)rows < cap ? (unsigned)rows : cap;
   if (D / 8 <= kNormVpt * kNormMaxThreads)

@@ -19,18 +19,20 @@ from .. import config
 from .._logging import utils as _log
 from ..ops import lib as _lib
 from ..parallel import symm_mem
-from .gemm_common import as_k_major_a, as_k_major_bt
+from .gemm_common import as_k_major_a, as_k_major_bt, use_tf32
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, **kwargs) -> torch.Tensor:
-    """Single-GPU C = A @ B on the library's tcgen05 kernel (bf16 inputs, fp32 accumulate).
+    """Single-GPU C = A @ B on the library's tcgen05 kernel (bf16 inputs, or fp32 inputs multiplied as
+    tf32; fp32 accumulate).
     Not in the reference's API; it is the compute core of every fused op, exposed for tests and
     roofline measurements. kwargs: swap_ab (-1 auto / 0 / 1), bn (column-tile override), max_ctas,
     pair (0 forces the single-CTA kernel; default lets large shapes use CTA pairs)."""
     if a.device.type != "cuda":
         return ref.matmul_f32(a, b).to(out_dtype)
-    a2, lda = as_k_major_a(a)
-    bt, ldb = as_k_major_bt(b)
+    tf32 = use_tf32(a, b) and kwargs.get("tf32", True)
+    a2, lda = as_k_major_a(a, tf32)
+    bt, ldb = as_k_major_bt(b, tf32)
     M, K = a2.shape
     N = bt.shape[0]
     if bt.shape[1] != K:
@@ -41,7 +43,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.bflo
     _lib.check(_lib.lib().kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
                                        1 if out_dtype == torch.float32 else 0, int(kwargs.get("swap_ab", -1)),
                                        int(kwargs.get("bn", 0)), int(kwargs.get("max_ctas", 0)),
-                                       int(kwargs.get("pair", 1)), _lib.current_stream_ptr()))
+                                       int(kwargs.get("pair", 1)), 1 if tf32 else 0, _lib.current_stream_ptr()))
     return out
 
 
@@ -213,22 +215,25 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     when the staging buffer has a multicast mapping); larger ones the two-shot form (tile owner
     t % ws receives all partials, sums them in rank order and publishes the result), which moves
     ws/2 times fewer bytes. Every rank gets identical bits. Decode-sized M puts the weights on the
-    128-row side of the MMA. kwargs: group, swap_ab, algo="one_shot"|"two_shot"."""
+    128-row side of the MMA. bf16 operands use the bf16 tensor-core path; fp32 x fp32 operands are
+    multiplied as tf32 (what ``tl.dot`` does for the reference's fp32 tests); anything else is cast
+    to bf16. kwargs: group, swap_ab, algo="one_shot"|"two_shot"."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_all_reduce(a, b, group)
-    a2, lda = as_k_major_a(a)
-    bt, ldb = as_k_major_bt(b)
+    tf32 = use_tf32(a, b)
+    a2, lda = as_k_major_a(a, tf32)
+    bt, ldb = as_k_major_bt(b, tf32)
     M, K = a2.shape
     N = bt.shape[0]
-    if bt.shape[1] != K or K % 8:
-        raise ValueError("inner dimensions must match and be a multiple of 8")
+    if bt.shape[1] != K or (K * a2.element_size()) % 16:
+        raise ValueError("inner dimensions must match and K rows must be whole 16-byte units")
     info = symm_mem.resolve_group(group)
     out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     L = _lib.lib()
     if info.world_size == 1:
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0, 1,
-                                  _lib.current_stream_ptr()))
+                                  1 if tf32 else 0, _lib.current_stream_ptr()))
         return out
     need = 2 * (info.world_size + 1) * M * N * 4
     hdl = symm_mem.get_symm_mem_workspace(group, need, a.device, kind="gemm_ar")
@@ -241,7 +246,8 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, mc, hdl.rank, hdl.world_size,
                                  a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
                                  int(kwargs.get("swap_ab", -1)), algo, calls & 1, config.TILE_FLAG_BASE,
-                                 hdl.signal_pad_words, hdl.buffer_size // 1024 * 1024, _lib.current_stream_ptr()))
+                                 hdl.signal_pad_words, hdl.buffer_size // 1024 * 1024, 1 if tf32 else 0,
+                                 _lib.current_stream_ptr()))
     return out
 
 
@@ -283,7 +289,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
     L = _lib.lib()
     s = _lib.current_stream_ptr()
     if ws == 1 and not (force and fused_ok):
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, s))
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, 0, s))
     elif fused_ok:
         if algo in ("pull", "scatter"):
             hdl = symm_mem.get_symm_mem_workspace(group, 2 * M * N * 2 + 2048, a.device, kind="gemm_rs")
@@ -302,7 +308,7 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
             raise ValueError("M * N must be a multiple of 8 * world size")
         hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
         stage = hdl.buffer_ptrs[hdl.rank]
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, 1, s))
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, stage, N, M, N, K, 0, 0, 0, 0, 1, 0, s))
         _lib.check(L.kr_reduce_scatter(hdl.buffer_ptrs_dev, 0, hdl.signal_pad_ptrs_dev, hdl.rank, ws, None,
                                        out.data_ptr(), M * N, 0, 0, s))
     return out if a.dtype != torch.float32 else out.to(a.dtype)
@@ -334,7 +340,7 @@ def gemm_reduce_scatter_ce_persistent(a: torch.Tensor, b: torch.Tensor, reduce_o
     dev = a.device
     out = torch.empty((M // ws, N), dtype=torch.bfloat16, device=dev)
     if ws == 1:
-        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1,
+        _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 0, -1, 0, 0, 1, 0,
                                   _lib.current_stream_ptr()))
         return out
     gemm_out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)

@@ -94,7 +94,7 @@ _PROTOS = {
     # gemm kernels
     "kr_tmap_cache_stats": (c_int, [POINTER(c_ulonglong), POINTER(c_ulonglong)]),
     "kr_gemm_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, _P]),
+                             c_int, c_int, c_int, _P]),
     "kr_ag_gemm_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int,
                                 c_int, _P, _P, c_int, c_uint32, c_int, c_ulonglong, c_uint32, c_ulonglong, c_int, _P]),
     "kr_gemm_rs_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
@@ -102,7 +102,7 @@ _PROTOS = {
     "kr_gemm_rs_set_trace": (c_int, [_P, c_ulonglong]),
     "kr_rs_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
     "kr_gemm_ar_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_uint32, c_ulonglong, c_ulonglong, _P]),
+                                c_int, c_int, c_int, c_int, c_uint32, c_ulonglong, c_ulonglong, c_int, _P]),
     "kr_gemm_ce_producer_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int,
                                          c_int, _P, _P, _P]),
     "kr_tile_order": (c_int, [c_int, c_int, c_int, c_int, c_int, _P]),

@@ -100,6 +100,28 @@ def test_gemm_row_major_b_and_fp32_inputs():
     assert torch.equal(c, c2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 520, 132), (16, 8192, 1024), (64, 1024, 512), (1, 2048, 64),
+                                   (2048, 2048, 1024)])
+def test_gemm_fp32_inputs_run_as_tf32(M, N, K):
+    # fp32 x fp32 operands are multiplied as tf32 (10-bit mantissa), fp32 accumulation, fp32 output
+    g = torch.Generator().manual_seed(21)
+    a = torch.randn(M, K, generator=g).cuda()
+    b = (0.05 * torch.randn(K, N, generator=g)).cuda()
+    ref = a.double() @ b.double()
+    c = fused.matmul(a, b, out_dtype=torch.float32)
+    tol = 2e-3 * 0.05 * (K ** 0.5)                     # 2^-11 per product, random signs
+    assert float((c.double() - ref).abs().max()) < tol
+    # and it is closer to the fp32 product than the bf16 path on the same data
+    c16 = fused.matmul(a, b, out_dtype=torch.float32, tf32=False)
+    assert float((c.double() - ref).abs().mean()) < float((c16.double() - ref).abs().mean())
+
+
+def test_gemm_tf32_exact_on_small_integers():
+    a = torch.randint(-8, 9, (384, 160)).float().cuda()
+    b = torch.randint(-8, 9, (160, 272)).float().cuda()
+    assert torch.equal(fused.matmul(a, b, out_dtype=torch.float32), a @ b)
+
+
 def test_gemm_persistent_many_tiles_per_cta():
     a, bt = _ab(2048, 2048, 256, seed=5)
     c = fused.matmul(a, bt.t(), max_ctas=7)         # 128 tiles over 7 CTAs: both accumulators, many rounds
@@ -264,6 +286,23 @@ def test_gemm_all_reduce_alternating_shapes_and_algorithms():
         outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo=algo))
         for r in range(ws):
             torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M", [1, 64, 256])
+def test_gemm_all_reduce_fp32_operands(M):
+    # the reference's GEMM + all-reduce tests feed fp32 operands (test/test_gemm_allreduce.py:57-58)
+    ws = 4
+    world = EmuWorld(ws)
+    N, Kl = 512, 128
+    g = torch.Generator().manual_seed(22)
+    a_s = [torch.randn(M, Kl, generator=g).cuda() for _ in range(ws)]
+    b_s = [(0.02 * torch.randn(Kl, N, generator=g)).cuda() for _ in range(ws)]
+    full = sum(a.double() @ b.double() for a, b in zip(a_s, b_s)).float()
+    for algo in ("one_shot", "two_shot"):
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], b_s[r], algo=algo))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
+            assert torch.equal(outs[0], outs[r])
 
 
 def test_gemm_all_reduce_rank_valued_exact():
