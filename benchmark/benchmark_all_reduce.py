@@ -66,6 +66,7 @@ def main():
             "one_shot": lambda: comm.one_shot_all_reduce(xs),
             "one_shot_pull": lambda: comm.one_shot_all_reduce(xs, algo="pull"),
             "two_shot": lambda: comm.two_shot_all_reduce(x),
+            "two_shot_p2p": lambda: comm.two_shot_all_reduce(x, nvls=False),
             "multimem": lambda: comm.multimem_all_reduce(xm),
             "nccl": lambda: dist.all_reduce(x.clone()),
         }

@@ -60,9 +60,20 @@ def main():
             "ar_bias_norm_one_shot": lambda: fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
             "nccl_add_norm": nccl_norm,
         }
+        def chain():
+            # the decode step this benchmark is about: GEMM + all-reduce, then the next layer's
+            # all-reduce + bias + RMSNorm, back to back on one stream
+            fused.gemm_one_shot_all_reduce_fused(a, b)
+            fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5)
+
+        backends["chain_gemm_ar_then_ar_bias_norm"] = chain
         if ref is not None and ((M + 63) // 64) * (N // 64) * ws <= 2304:
+            # same bf16 operands as this library's column; the fp32 column is how the reference's own
+            # test feeds it (test/test_gemm_allreduce.py:57-58) and moves twice the bytes
+            bc = b.contiguous()
+            backends["ref_gemm_ar"] = lambda: ref.fused.gemm_one_shot_all_reduce_fused(a, bc)
             af, bf = a.float(), b.float().contiguous()
-            backends["ref_gemm_ar"] = lambda: ref.fused.gemm_one_shot_all_reduce_fused(af, bf)
+            backends["ref_gemm_ar_fp32"] = lambda: ref.fused.gemm_one_shot_all_reduce_fused(af, bf)
         row = {"M": M, "K_per_rank": Kl, "N": N,
                "weight_read_us": Kl * N * 2 / (pk["hbm_gbs"] * 1e9) * 1e6}
         for name, fn in backends.items():

@@ -169,6 +169,8 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
             off = None
         calls = getattr(oh, "_ag_calls", 0)
         oh._ag_calls = calls + 1
+        if symm_mem.capturing():
+            calls, barrier = 0, 1       # a replayed graph repeats one half / flag bank: protect it with the entry barrier
         if off is None:
             off = (calls & 1) * half
             gathered = oh.get_buffer(rank, (M, K), torch.bfloat16, storage_offset=off // 2)
@@ -240,6 +242,8 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     calls = getattr(hdl, "_gemm_ar_calls", 0)      # per staging buffer: selects the staging half / flag bank
     hdl._gemm_ar_calls = calls + 1
     algo = {"one_shot": 0, "two_shot": 1}.get(str(kwargs.get("algo", config.force_algo() or "")), -1)
+    if symm_mem.capturing():
+        algo = 1                        # one-shot alternates staging halves call by call: not replayable
     mc = hdl.multicast_ptr or None
     _log.log_kernel_choice("gemm_one_shot_all_reduce", f"M={M} N={N} K={K} ws={hdl.world_size} "
                            f"exchange={('by size', 'one_shot', 'two_shot')[algo + 1]} nvls={bool(mc)}")
@@ -280,6 +284,8 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
     algo = str(kwargs.get("algo", config.rs_algo()))
     if algo not in ("pull", "push", "scatter"):
         raise ValueError("algo must be 'pull', 'scatter' or 'push'")
+    if symm_mem.capturing() and algo != "push":
+        algo = "push"                   # pull and scatter alternate staging halves call by call: not replayable
     fused_ok = (M // ws) % 128 == 0 and N % 8 == 0 and N >= 256
     force = bool(kwargs.get("_force_fused", False))           # tests: run the fused kernel at world size 1
     if _log.dump_enabled():

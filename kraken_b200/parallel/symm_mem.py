@@ -528,6 +528,17 @@ class EmuWorld:
         return outs
 
 
+def capturing() -> bool:
+    """True while the current stream is being captured into a CUDA graph. Ops that alternate two
+    buffer halves / flag banks from call to call (so that they need no barrier) must not do so
+    under capture: a replayed graph repeats the SAME half every time, so they switch to their
+    barrier-protected variants instead."""
+    try:
+        return bool(torch.cuda.is_current_stream_capturing())
+    except Exception:
+        return False
+
+
 def reset_signal_pads(handle: SymmHandle) -> None:
     """Recovery after a reported timeout: a wait that gave up can leave tokens behind in the
     signal pads. Collective over the handle's group: every rank zeroes its own pad between two

@@ -62,6 +62,14 @@ def _all_ops(rank, ws):
     for _ in range(3):
         torch.testing.assert_close(comm.one_shot_all_reduce(xs).float(), gold, atol=1e-1, rtol=1e-1)
         torch.testing.assert_close(comm.two_shot_all_reduce(x).float(), gold, atol=1e-1, rtol=1e-1)
+        torch.testing.assert_close(comm.two_shot_all_reduce(x, nvls=False).float(), gold, atol=1e-1, rtol=1e-1)
+        torch.testing.assert_close(comm.one_shot_all_reduce(xs, algo="pull").float(), gold, atol=1e-1, rtol=1e-1)
+    small = symm_mem.empty(5120, dtype=torch.bfloat16, device=dev)       # push-sized message
+    small.copy_(x.view(-1)[:5120])
+    gold_small = nccl_sum(small)
+    for _ in range(4):
+        for algo in ("push", "pull"):
+            torch.testing.assert_close(comm.one_shot_all_reduce(small, algo=algo).float(), gold_small, atol=1e-1, rtol=1e-1)
     z = symm_mem.empty(1024, 1024, dtype=torch.bfloat16, device=dev)
     z.copy_(x)
     symm_mem.rendezvous(z)
@@ -111,6 +119,12 @@ def _all_ops(rank, ws):
                 y = torch.empty_like(xb)
                 fn(pad, xb, bb, w, y, 1e-5)
                 torch.testing.assert_close(y.float(), goldn, atol=4e-2, rtol=4e-2)
+            y = torch.empty_like(xb)
+            fused.one_shot_all_reduce_bias_rms_norm(pad, xb, bb, w, y, 1e-5, algo="pull")
+            torch.testing.assert_close(y.float(), goldn, atol=4e-2, rtol=4e-2)
+            out3 = torch.empty_like(xb)
+            fused.one_shot_all_reduce_bias(pad, xb, bb, out3, algo="pull")
+            torch.testing.assert_close(out3.float(), s + bb.float(), atol=5e-2, rtol=5e-2)
     # -- all-gather matmul (reference: test/test_allgather_matmul.py, scaled down)
     Ml, K, N = 1024, 2048, 1536
     a_sh = symm_mem.empty(Ml, K, dtype=torch.bfloat16, device=dev)
@@ -170,6 +184,44 @@ def _all_ops(rank, ws):
     o = fused.gemm_one_shot_all_reduce_fused(ones * (rank + 1), ones)
     expect = 32.0 * sum(range(1, ws + 1))
     torch.testing.assert_close(o, torch.full((32, 32), expect, device=dev), atol=1e-5, rtol=1e-5)
+    # -- CUDA-graph replay across ranks: under capture the ops that alternate buffer halves from
+    #    call to call switch to their barrier-protected forms, so a replayed graph stays correct
+    xg = symm_mem.empty(4096, dtype=torch.bfloat16, device=dev)
+    xg.copy_(torch.randn(4096, device=dev).to(torch.bfloat16))
+    ag_in = symm_mem.empty(256, 512, dtype=torch.bfloat16, device=dev)
+    ag_in.copy_(torch.randn(256, 512, device=dev).to(torch.bfloat16))
+    wg = (0.05 * torch.randn(384, 512, device=dev)).to(torch.bfloat16)
+    a_g = torch.randn(256 * ws, 256, device=dev).to(torch.bfloat16)
+    bt_g = (0.05 * torch.randn(512, 256, device=dev)).to(torch.bfloat16)
+
+    def graph_body():
+        r1 = comm.one_shot_all_reduce(xg)
+        _, r2 = fused.all_gather_matmul(ag_in, wg.t())
+        r3 = fused.gemm_reduce_scatter(a_g, bt_g.t())
+        r4 = fused.gemm_one_shot_all_reduce_fused(a_g[:16], bt_g.t())
+        return r1, r2, r3, r4
+
+    eager = [t.clone() for t in graph_body()]          # also: first-use set-up (rendezvous, workspaces) outside capture
+    torch.cuda.synchronize()
+    dist.barrier()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            graph_body()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    cg = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(cg):
+        captured = graph_body()
+    for _ in range(4):
+        cg.replay()
+    torch.cuda.synchronize()
+    for got, want in zip(captured, eager):
+        torch.testing.assert_close(got.float(), want.float(), atol=5e-2, rtol=5e-2)
+    kraken_b200.check_status()
+    dist.barrier()
     # -- the model block
     mlp = kraken_b200.models.TPMLP(hidden=1024, ffn=2048 * ws, device=dev, seed=11)
     xm = mlp.stage_input(torch.randn(256, 1024, device=dev).to(torch.bfloat16))
