@@ -389,6 +389,11 @@ def get_symm_mem_workspace(group=None, min_size: int = 0, device=None, kind: str
     hdl = _workspaces.get(key)
     if hdl is not None and hdl.buffer_size >= min_size:
         return hdl
+    if capturing():
+        raise RuntimeError(f"the '{kind}' symmetric workspace ({min_size} bytes) has to exist before CUDA-graph capture: "
+                           "growing it is a collective with host synchronisation. Call "
+                           "symm_mem.get_symm_mem_workspace(group, size, kind=...) or run the op once eagerly first "
+                           "(note that under capture some ops use another variant, see symm_mem.capturing)")
     size = max(int(min_size), int(os.environ.get("KRAKEN_WS_MIN_MB", "32")) << 20)
     size = 1 << (size - 1).bit_length()      # geometric growth: few re-rendezvous
     pre = int(os.environ.get("KRAKEN_WS_PREALLOC_MB", "0"))
