@@ -94,6 +94,23 @@ def _all_ops(rank, ws):
             torch.cuda.synchronize()
             assert torch.equal(ag, gold_ag), (backend, splits)
             assert bool((prog.to(torch.int64) != 0).all())
+    # -- the allocation-free all-gather entry point across real ranks (built-in counters and status word)
+    import ctypes
+
+    from kraken_b200.ops import lib as klib
+
+    hx = symm_mem.rendezvous(xs)
+    rd_word = ctypes.c_uint32(1)
+    for _ in range(2):
+        ag_na = torch.full_like(gold_ag, float("nan"))
+        prog_na = torch.zeros(ws * 4, dtype=torch.uint32, device=dev)
+        klib.check(klib.lib().kr_all_gather_sm_noalloc(hx.buffer_ptrs_dev, hx.offset_of(xs), hx.signal_pad_ptrs_dev, rank, ws,
+                                                       ag_na.data_ptr(), prog_na.data_ptr(), 4, xs.numel(), 0, 0, None,
+                                                       klib.current_stream_ptr()))
+        klib.check(klib.lib().kr_noalloc_read_status(klib.current_stream_ptr(), ctypes.byref(rd_word), 0))
+        assert rd_word.value == 0
+        assert torch.equal(ag_na, gold_ag) and bool((prog_na.to(torch.int64) == 1).all())
+    dist.barrier()
     # -- bias and bias + RMSNorm epilogues (reference: test/test_allreduce_bias*.py)
     pad = symm_mem.empty(1024, 1024, dtype=torch.bfloat16, device=dev)
     symm_mem.rendezvous(pad)
