@@ -1,18 +1,14 @@
-// tcgen05 GEMM kernels: plain GEMM and the three fused GEMM + collective kernels.
+// tcgen05 GEMM kernels: the plain GEMM, the fused all-gather -> GEMM and the producer GEMM of the
+// copy-engine reduce-scatter, plus the host-side pieces every GEMM translation unit shares (tensor-map
+// cache, operand set-up, tile-order defaults). The reduce-scatter GEMMs live in gemm_rs.cu, the
+// decode GEMM -> all-reduce in gemm_ar.cu, the tf32 kernels in gemm_tf32.cu.
 //
-//  * all-gather -> GEMM (reference: kraken/fused/all_gather_matmul.py:222-325): a few comm CTAs
-//    pull the peers' A shards into the local gathered buffer with 1-D bulk async copies and
-//    publish per-chunk progress flags; the MMA CTAs start on the local shard (rank pivot) and
-//    consume remote chunks as their flags appear. One launch, no copy engine, no second stream.
-//  * GEMM -> reduce-scatter (reference: kraken/fused/gemm_reduce_scatter_fused.py:152-235 and
-//    gemm_reduce_scatter_ce_persistent.py:326-375): the epilogue pushes each finished tile straight
-//    into the OWNER rank's staging slab over NVLink and bumps a per-tile flag there. Every rank
-//    computes its own slab last; the epilogue of those tiles waits for the tile's flag, adds the
-//    peers' staged partial sums to the accumulator fragment in rank order (bitwise reproducible)
-//    and writes the final rows — there is no separate reduction pass.
-//  * GEMM -> all-reduce for decode (reference: kraken/fused/gemm_one_shot_all_reduce_fused.py:106-178):
-//    fp32 partial tile to the own staging buffer, per-tile flags to all peers, then each rank sums
-//    the tile from all ranks in rank order into its fp32 output.
+//  * all-gather -> GEMM (reference: kraken/fused/all_gather_matmul.py:222-325): comm CTAs of the
+//    same launch move the shards (push: the own shard into every peer's gathered buffer with posted
+//    bulk stores; pull: the peers' shards into the local one) and raise per-chunk flags; the MMA
+//    CTAs start on the local shard (rank pivot) and consume remote chunks as their flags appear.
+//    One launch, no copy engine, no second stream. A copy-engine feed is available as well.
+//  * copy-engine reduce-scatter producer (reference: gemm_reduce_scatter_ce_persistent.py:46-134).
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -277,12 +273,8 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
       gemm_mainloop<BN>(p, bid, n_mma, h, smem_raw);
     }
     if (p.ag_push) ag_push_finish(p, nb);
-  } else if (p.mode == GEMM_CE) {
-    CeHooks h;
-    h.bn = BN;
-    gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   } else {
-    ArHooks h;
+    CeHooks h;
     h.bn = BN;
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   }
@@ -413,7 +405,7 @@ bool store_tmap(const void* ptr, long long rows, long long cols, long long ld, C
   return get_tmap(ptr, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, 32, m) == KR_SUCCESS;
 }
 
-static int pick_bn(int rows_c) {
+int pick_bn(int rows_c) {
   if (rows_c > 128) return 256;
   if (rows_c > 64) return 128;
   if (rows_c > 32) return 64;
@@ -422,7 +414,7 @@ static int pick_bn(int rows_c) {
 }
 
 // The tf32 kernels exist for three column-tile widths.
-static int tf32_bn(int rows_c) { return rows_c <= 16 ? 16 : (rows_c <= 64 ? 64 : 256); }
+int tf32_bn(int rows_c) { return rows_c <= 16 ? 16 : (rows_c <= 64 ? 64 : 256); }
 
 constexpr size_t kAgSmem = (size_t)kAgSlots * kAgPiece + 1024 + 128;
 static_assert(kAgSmem <= (size_t)kSmemLimit, "comm ring exceeds shared memory");
@@ -478,8 +470,9 @@ static int launch_pair(GemmParams p, unsigned cap, unsigned n_comm, cudaStream_t
   return KR_SUCCESS;
 }
 
-static int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream) {
+int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream) {
   if (p.in_fp32) return launch_gemm_tf32(bn, p, nb, stream);
+  if (p.mode == GEMM_AR) return launch_gemm_ar(bn, p, nb, stream);
   const size_t floor_smem = p.mode == GEMM_AG ? kAgSmem : 0;   // comm CTAs reuse the block's shared memory
   auto sm = [&](size_t s) { return s > floor_smem ? s : floor_smem; };
   switch (bn) {
@@ -650,75 +643,6 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   if (n_mma > cap - n_comm) n_mma = cap - n_comm;
   p.num_mma_ctas = (int)n_mma;
   return launch_gemm(bn, p, n_mma + n_comm, stream);
-}
-
-// Fused GEMM -> all-reduce (decode). bufs[r] = rank r's staging buffer of staging_bytes, DEDICATED
-// to this op (nothing else may write it between calls); needs staging_bytes >= 2*(ws+1)*M*N*4.
-// out[M, N] fp32 =
-// sum_r a_r[M, K_local] * bt_r[N, K_local]^T. algo: 0 one-shot, 1 two-shot, -1 by size.
-// call_parity: 0/1, alternating from call to call on the same staging buffer.
-KR_API int kr_gemm_ar_bf16(void* const* bufs, uint32_t* const* pads, void* mc_ptr, int rank, int ws, const void* a,
-                           long long lda, const void* bt, long long ldb, void* out, long long ldo, int M, int N, int K,
-                           int swap_ab, int algo, int call_parity, uint32_t flag_base, unsigned long long pad_words,
-                           unsigned long long staging_bytes, int in_fp32, cudaStream_t stream) {
-  DeviceState* d = device_state();
-  if (!d) return KR_FAIL_CUDA;
-  KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  const bool swap = swap_ab < 0 ? (M <= 64 && N >= 128) : swap_ab != 0;
-  // column tile: as many CTAs as the problem allows (up to one per SM), tiles no wider than needed
-  const int rows_c = swap ? M : N;
-  const int tiles_r = ((swap ? N : M) + kBM - 1) / kBM;
-  int bn_pick = pick_bn(rows_c);
-  while (bn_pick > 16 && tiles_r * ((rows_c + bn_pick - 1) / bn_pick) < d->num_sms / 2 &&
-         tiles_r * ((rows_c + bn_pick / 2 - 1) / (bn_pick / 2)) <= d->num_sms)
-    bn_pick /= 2;
-  if (in_fp32) bn_pick = bn_pick <= 16 ? 16 : (bn_pick <= 64 ? 64 : 256);
-  int bn = 0;
-  int rc = setup_problem(p, a, lda, bt, ldb, M, N, K, swap, bn_pick, &bn, in_fp32 ? 4 : 2);
-  if (rc) return rc;
-  p.mode = GEMM_AR;
-  p.out = out;
-  p.ldo = ldo;
-  p.out_rows = M;
-  p.out_cols = N;
-  p.out_fp32 = 1;
-  p.rank = rank;
-  p.ws = ws;
-  p.bufs = bufs;
-  p.pads = pads;
-  p.mc_ptr = mc_ptr;
-  const unsigned long long mn4 = (unsigned long long)M * N * 4;
-  const int tiles = p.tiles_r * p.tiles_c;
-  if (algo < 0) algo = ((unsigned long long)(ws - 1) * mn4 > (1ull << 20)) ? 1 : 0;   // > 1 MiB of pull traffic
-  p.ar_algo = algo;
-  // Fixed layout of the dedicated staging buffer (S bytes) and of the flag words, independent of the
-  // problem shape, so that consecutive calls of different shapes or algorithms never share a region
-  // a slower rank may still be reading:
-  //   [0, S/4) one-shot even calls | [S/4, S/2) one-shot odd calls | [S/2, S) two-shot partial slots + result
-  //   flag words: one-shot even | +50000 one-shot odd | +100000 two-shot "partial stored" | +150000 "published"
-  const unsigned long long S = staging_bytes;
-  KR_REQUIRE(S % 1024 == 0, "staging size must be a multiple of 1024 bytes");
-  KR_REQUIRE(tiles <= 50000 && (unsigned long long)flag_base + 200000ull <= pad_words,
-             "signal pad too small for the tile flags");
-  if (algo == 0) {
-    KR_REQUIRE(S / 4 >= mn4, "staging buffer too small for one-shot GEMM all-reduce");
-    p.stage_off = (call_parity & 1) ? S / 4 : 0;
-    p.flag_base = flag_base + ((call_parity & 1) ? 50000u : 0u);
-  } else {
-    KR_REQUIRE(S / 2 >= (unsigned long long)(ws + 1) * mn4, "staging buffer too small for two-shot GEMM all-reduce");
-    p.part_off = S / 2;
-    p.res_off = S / 2 + (unsigned long long)ws * mn4;
-    p.flag_base = flag_base + 100000u;
-    p.flag2_base = flag_base + 150000u;
-  }
-  p.sync = sync_ctx(d);
-  unsigned nb = (unsigned)tiles;
-  unsigned cap = grid_cap(d);
-  if (nb > cap) nb = cap;
-  p.num_mma_ctas = (int)nb;
-  return launch_gemm(bn, p, nb, stream);
 }
 
 // Producer GEMM of the copy-engine reduce-scatter variant: gemm_out[M, N] = a * bt^T on this GPU;

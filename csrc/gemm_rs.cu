@@ -159,7 +159,9 @@ struct RsPullHooks : HookDefaults {
   }
 
   // Sum with plain loads: B vectors per thread, all W >= ws ranks' loads of all of them in flight
-  // together; adds in rank order (every call gives the same bits).
+  // together (B * W = 8 requests per thread: sixteen made the register allocator spill the loaded
+  // values, which turns every load into a synchronous one); adds in rank order (every call gives
+  // the same bits).
   template <int B, int W>
   __device__ __forceinline__ void reduce_loads(const GemmParams& p, int tid, int total, int vpr, int lrow0, int col0) {
     for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * B) {
@@ -193,8 +195,9 @@ struct RsPullHooks : HookDefaults {
   // One work item: rows [sub*rs_sub_rows, +rs_sub_rows) of 128-row tile (tr, tc) of the own slab, summed over all
   // ranks into `out`. Thread tid of 128 handles 16-byte vectors tid, tid + 128, ...: a warp covers
   // one 512-byte row segment per instruction. The item that finishes a tile last puts the tile's
-  // counters back to zero.
-  __device__ __forceinline__ bool reduce_item(const GemmParams& p, int tr, int tc, int sub, int tid, int slot) {
+  // counters back to zero. Not inlined: the reducer warps get their own register allocation
+  // instead of sharing the epilogue's.
+  __device__ __noinline__ bool reduce_item(const GemmParams& p, int tr, int tc, int sub, int tid, int slot) {
     uint32_t* f = counter(p, p.rank, tr, tc);
     uint32_t* done = f + p.rs_done_off;
     const uint32_t need = (uint32_t)p.ws;
@@ -238,11 +241,11 @@ struct RsPullHooks : HookDefaults {
         }
       }
     } else if (p.ws <= 2) {
-      reduce_loads<8, 2>(p, tid, total, vpr, lrow0, col0);
+      reduce_loads<4, 2>(p, tid, total, vpr, lrow0, col0);
     } else if (p.ws <= 4) {
-      reduce_loads<4, 4>(p, tid, total, vpr, lrow0, col0);
+      reduce_loads<2, 4>(p, tid, total, vpr, lrow0, col0);
     } else {
-      reduce_loads<2, 8>(p, tid, total, vpr, lrow0, col0);
+      reduce_loads<1, 8>(p, tid, total, vpr, lrow0, col0);
     }
     reducer_bar_sync();                        // every thread's loads of this item have returned
     if (tid == 0) {

@@ -22,5 +22,11 @@ int setup_problem(GemmParams& p, const void* a, long long lda, const void* bt, l
 // Single-CTA kernels for fp32 operands multiplied as tf32 (plain GEMM and GEMM -> all-reduce;
 // column tiles of 16, 64 or 256). Defined in gemm_tf32.cu.
 int launch_gemm_tf32(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream);
+// Single-CTA kernels of the decode GEMM -> all-reduce. Defined in gemm_ar.cu.
+int launch_gemm_ar(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream);
+// Routes a parameter block to the kernel family of its mode and operand type (gemm.cu).
+int launch_gemm(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream);
+int pick_bn(int rows_c);      // column-tile width for `rows_c` rows of the column operand
+int tf32_bn(int rows_c);      // the same among the widths the tf32 kernels exist for
 
 }  // namespace kraken

@@ -7,7 +7,7 @@
 namespace kraken {
 
 constexpr int kNormMaxThreads = 1024;
-constexpr int kNormVpt = 4;   // 16-byte vectors a thread keeps in registers per row
+constexpr int kNormVpt = 4;   // most 16-byte vectors a thread keeps in registers per row
 
 __device__ __forceinline__ float block_sum(float v, float* smem) {
   v = warp_sum(v);
@@ -20,11 +20,12 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 }
 
 // Normalises the row held in f[][] (vectors threadIdx.x + i*blockDim.x) and writes it to yrow.
-__device__ __forceinline__ void rms_finish(float (&f)[kNormVpt][8], int nvec, int D, float eps, const char* w,
+template <int VPT>
+__device__ __forceinline__ void rms_finish(float (&f)[VPT][8], int nvec, int D, float eps, const char* w,
                                            char* yrow, float* smem) {
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < kNormVpt; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
 #pragma unroll
@@ -34,7 +35,7 @@ __device__ __forceinline__ void rms_finish(float (&f)[kNormVpt][8], int nvec, in
   ss = block_sum(ss, smem);
   const float inv = rsqrtf(ss / (float)D + eps);
 #pragma unroll
-  for (int i = 0; i < kNormVpt; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
       float g[8];

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kNormMaxThreads) rms_norm_kernel(const __grid_
         if (v < nvec) nx[i] = ld16(xrow + (size_t)v * 16);
       }
     }
-    rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + (size_t)r * p.D * 2, smem);
+    rms_finish<kNormVpt>(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + (size_t)r * p.D * 2, smem);
   }
 }
 
@@ -100,7 +100,11 @@ __device__ __forceinline__ void norm_add_bias8(const NormParams& p, size_t elem,
 }
 
 // ---- one-shot all-reduce + bias + RMSNorm ------------------------------------------------------
-__device__ void ar_norm_one_shot_body(const NormParams& p, unsigned bid, unsigned nb) {
+// VPT: vectors a thread keeps per row. 1 covers rows of up to 8192 elements with every peer's load
+// of the thread's vector in flight at once and no register spills (a spilled load becomes a
+// synchronous one: ws NVLink round trips instead of one).
+template <int VPT>
+__device__ __forceinline__ void ar_norm_one_shot_impl(const NormParams& p, unsigned bid, unsigned nb) {
   __shared__ float smem[32];
   const int nvec = p.D / 8;
   const uint32_t sync_id = p.pad_base / p.ws + bid;
@@ -113,9 +117,9 @@ __device__ void ar_norm_one_shot_body(const NormParams& p, unsigned bid, unsigne
   if (!symm_mem_sync<true, true>(p.pads, sync_id, p.rank, p.ws, p.sync, 30)) return;
   for (int r = bid; r < p.rows; r += nb) {
     const size_t off = (size_t)r * p.D * 2;
-    float f[kNormVpt][8];
+    float f[VPT][8];
 #pragma unroll
-    for (int i = 0; i < kNormVpt; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
 #pragma unroll
@@ -137,16 +141,19 @@ __device__ void ar_norm_one_shot_body(const NormParams& p, unsigned bid, unsigne
         }
       }
     }
-    rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + off, smem);
+    rms_finish<VPT>(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + off, smem);
   }
   symm_mem_sync<true, false>(p.pads, sync_id, p.rank, p.ws, p.sync, 31);
 }
+__device__ void ar_norm_one_shot_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_one_shot_impl<1>(p, bid, nb); }
+__device__ void ar_norm_one_shot_long_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_one_shot_impl<kNormVpt>(p, bid, nb); }
+KR_DEFINE_RANKED_KERNEL(ar_norm_one_shot_long, NormParams, kNormMaxThreads)
 KR_DEFINE_RANKED_KERNEL(ar_norm_one_shot, NormParams, kNormMaxThreads)
 
 // ---- two-shot all-reduce + bias + RMSNorm ------------------------------------------------------
 // Rank k reduces columns [k*D/ws, (k+1)*D/ws) of every row the block owns (+bias), publishes the
 // bf16 sums to all ranks (P2P stores, or one multimem.st), then each rank normalises its rows.
-template <bool USE_MC>
+template <bool USE_MC, int VPT>
 __device__ __forceinline__ void ar_norm_two_shot_impl(const NormParams& p, unsigned bid, unsigned nb) {
   __shared__ float smem[32];
   const int nvec = p.D / 8;
@@ -201,20 +208,24 @@ __device__ __forceinline__ void ar_norm_two_shot_impl(const NormParams& p, unsig
   if (!symm_mem_sync<true, true>(p.pads, sync_id, p.rank, p.ws, p.sync, 33)) return;
   for (int r = bid; r < p.rows; r += nb) {
     const size_t off = (size_t)r * p.D * 2;
-    float f[kNormVpt][8];
+    float f[VPT][8];
 #pragma unroll
-    for (int i = 0; i < kNormVpt; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) unpack8(ld16(own + off + (size_t)v * 16), f[i]);
     }
-    rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + off, smem);
+    rms_finish<VPT>(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.y + off, smem);
   }
   symm_mem_sync<true, false>(p.pads, sync_id, p.rank, p.ws, p.sync, 34);
 }
-__device__ void ar_norm_two_shot_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<false>(p, bid, nb); }
-__device__ void ar_norm_two_shot_mc_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<true>(p, bid, nb); }
+__device__ void ar_norm_two_shot_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<false, 1>(p, bid, nb); }
+__device__ void ar_norm_two_shot_mc_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<true, 1>(p, bid, nb); }
+__device__ void ar_norm_two_shot_long_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<false, kNormVpt>(p, bid, nb); }
+__device__ void ar_norm_two_shot_mc_long_body(const NormParams& p, unsigned bid, unsigned nb) { ar_norm_two_shot_impl<true, kNormVpt>(p, bid, nb); }
 KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot, NormParams, kNormMaxThreads)
 KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot_mc, NormParams, kNormMaxThreads)
+KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot_long, NormParams, kNormMaxThreads)
+KR_DEFINE_RANKED_KERNEL(ar_norm_two_shot_mc_long, NormParams, kNormMaxThreads)
 
 }  // namespace kraken
 
@@ -283,7 +294,13 @@ KR_API int kr_all_reduce_bias_rms_norm(void* const* bufs, unsigned long long buf
   if (emu_recorder().active) cap = cap / (unsigned)emu_recorder().ws ? cap / (unsigned)emu_recorder().ws : 1;
   unsigned nb = (unsigned)rows < cap ? (unsigned)rows : cap;
   unsigned nt = norm_threads(D, 1);
-  if (algo == 0) return launch_ranked(ar_norm_one_shot_kernel, ar_norm_one_shot_emu_kernel, p, nb, nt, 0, stream);
-  if (algo == 1) return launch_ranked(ar_norm_two_shot_kernel, ar_norm_two_shot_emu_kernel, p, nb, nt, 0, stream);
-  return launch_ranked(ar_norm_two_shot_mc_kernel, ar_norm_two_shot_mc_emu_kernel, p, nb, nt, 0, stream);
+  const bool longrow = (unsigned)D / 8 > nt;       // more than one vector per thread
+  if (algo == 0)
+    return longrow ? launch_ranked(ar_norm_one_shot_long_kernel, ar_norm_one_shot_long_emu_kernel, p, nb, nt, 0, stream)
+                   : launch_ranked(ar_norm_one_shot_kernel, ar_norm_one_shot_emu_kernel, p, nb, nt, 0, stream);
+  if (algo == 1)
+    return longrow ? launch_ranked(ar_norm_two_shot_long_kernel, ar_norm_two_shot_long_emu_kernel, p, nb, nt, 0, stream)
+                   : launch_ranked(ar_norm_two_shot_kernel, ar_norm_two_shot_emu_kernel, p, nb, nt, 0, stream);
+  return longrow ? launch_ranked(ar_norm_two_shot_mc_long_kernel, ar_norm_two_shot_mc_long_emu_kernel, p, nb, nt, 0, stream)
+                 : launch_ranked(ar_norm_two_shot_mc_kernel, ar_norm_two_shot_mc_emu_kernel, p, nb, nt, 0, stream);
 }

@@ -88,9 +88,11 @@ __device__ void push_ar_body(const PushParams& p, unsigned bid, unsigned nb) {
 KR_DEFINE_RANKED_KERNEL(push_ar, PushParams, kPushThreads)
 
 // ---- all-reduce + bias + RMSNorm --------------------------------------------------------------
-// One block per row (row r -> block r % nb on every rank); a thread keeps up to kNormVpt vectors
-// of the row in registers from the push to the normalisation.
-__device__ void push_ar_norm_body(const PushParams& p, unsigned bid, unsigned nb) {
+// One block per row (row r -> block r % nb on every rank); a thread keeps VPT vectors of the row
+// in registers from the push to the normalisation (1 for rows of up to 8192 elements: no spills, all
+// ws slot loads of the vector in flight together).
+template <int VPT>
+__device__ __forceinline__ void push_ar_norm_impl(const PushParams& p, unsigned bid, unsigned nb) {
   __shared__ float smem[32];
   const int nvec = p.D / 8;
   // phase 1: all rows of this block go out before the barrier
@@ -104,9 +106,9 @@ __device__ void push_ar_norm_body(const PushParams& p, unsigned bid, unsigned nb
   if (!symm_mem_sync<true, true>(p.pads, p.pad_base / p.ws + bid, p.rank, p.ws, p.sync, 61)) return;
   for (int r = bid; r < p.rows; r += nb) {
     const size_t off = (size_t)r * p.D * 2;
-    float f[kNormVpt][8];
+    float f[VPT][8];
 #pragma unroll
-    for (int i = 0; i < kNormVpt; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
         const size_t bo = off + (size_t)v * 16;
@@ -116,9 +118,12 @@ __device__ void push_ar_norm_body(const PushParams& p, unsigned bid, unsigned nb
         gather_vec(p, bo, ld16((const char*)p.input + bo), f[i]);
       }
     }
-    rms_finish(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.output + off, smem);
+    rms_finish<VPT>(f, nvec, p.D, p.eps, (const char*)p.w, (char*)p.output + off, smem);
   }
 }
+__device__ void push_ar_norm_body(const PushParams& p, unsigned bid, unsigned nb) { push_ar_norm_impl<1>(p, bid, nb); }
+__device__ void push_ar_norm_long_body(const PushParams& p, unsigned bid, unsigned nb) { push_ar_norm_impl<kNormVpt>(p, bid, nb); }
+KR_DEFINE_RANKED_KERNEL(push_ar_norm_long, PushParams, kNormMaxThreads)
 KR_DEFINE_RANKED_KERNEL(push_ar_norm, PushParams, kNormMaxThreads)
 
 }  // namespace kraken
@@ -211,5 +216,6 @@ KR_API int kr_push_all_reduce_bias_rms_norm(void* const* bufs_host, uint32_t* co
   unsigned nt = ((unsigned)D / 8 + 31) / 32 * 32;      // one vector per thread when the row allows
   if (nt < 64) nt = 64;
   if (nt > kNormMaxThreads) nt = kNormMaxThreads;
+  if ((unsigned)D / 8 > nt) return launch_ranked(push_ar_norm_long_kernel, push_ar_norm_long_emu_kernel, p, nb, nt, 0, stream);
   return launch_ranked(push_ar_norm_kernel, push_ar_norm_emu_kernel, p, nb, nt, 0, stream);
 }

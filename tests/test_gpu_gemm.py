@@ -109,7 +109,7 @@ def test_gemm_fp32_inputs_run_as_tf32(M, N, K):
     b = (0.05 * torch.randn(K, N, generator=g)).cuda()
     ref = a.double() @ b.double()
     c = fused.matmul(a, b, out_dtype=torch.float32)
-    tol = 2e-3 * 0.05 * (K ** 0.5)                     # 2^-11 per product, random signs
+    tol = 1e-2 * 0.05 * (K ** 0.5)                     # operands cut to 10 mantissa bits, random signs, max over the matrix
     assert float((c.double() - ref).abs().max()) < tol
     # and it is closer to the fp32 product than the bf16 path on the same data
     c16 = fused.matmul(a, b, out_dtype=torch.float32, tf32=False)
