@@ -5,7 +5,7 @@
 //
 //  * pull: every rank TMA-stores ALL its partial tiles into its OWN symmetric staging matrix
 //    [M][N] (local traffic only, the epilogue never touches NVLink) and bumps a per-tile arrival
-//    counter in the tile owner's signal pad. Four extra "reducer" warps per CTA serve the tiles this
+//    counter in the tile owner's signal pad. Six extra "reducer" warps per CTA serve the tiles this
 //    rank owns, in work items of 16 rows dealt round-robin to all CTAs: wait until all ws ranks have
 //    stored the tile, then sum it across ranks with ws peer loads in rank order (or in the NVSwitch
 //    with multimem.ld_reduce when asked to) and write the final rows.
@@ -25,10 +25,10 @@
 
 namespace kraken {
 
-constexpr int kRsReducerThreads = 128;
+constexpr int kRsReducerThreads = 192;   // six warps: with 12 warps per CTA the register budget per thread is the same as with 10
 constexpr int kRsPullThreads = kGemmThreads + kRsReducerThreads;
 
-__device__ __forceinline__ void reducer_bar_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void reducer_bar_sync() { asm volatile("bar.sync 2, 192;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // push: remote tiles go to the owner's staging slab, own tiles reduce in the epilogue
@@ -193,7 +193,7 @@ struct RsPullHooks : HookDefaults {
   }
 
   // One work item: rows [sub*rs_sub_rows, +rs_sub_rows) of 128-row tile (tr, tc) of the own slab, summed over all
-  // ranks into `out`. Thread tid of 128 handles 16-byte vectors tid, tid + 128, ...: a warp covers
+  // ranks into `out`. Thread tid of 192 handles 16-byte vectors tid, tid + 192, ...: a warp covers
   // one 512-byte row segment per instruction. The item that finishes a tile last puts the tile's
   // counters back to zero. Not inlined: the reducer warps get their own register allocation
   // instead of sharing the epilogue's.
@@ -258,34 +258,42 @@ struct RsPullHooks : HookDefaults {
     return true;
   }
 
-  // Reducer warps: walk the tile order, number the work items of the own slab's tiles in that
-  // order (a pair tile: upper half first) and serve every num_ctas-th of them.
+  // Reducer warps: walk the OWN tiles of the interleaved tile order in order (same sequence as
+  // tile_coords with pivot 0: row groups, inside a group column by column, inside a column the
+  // group's rows; virtual row v belongs to rank v % ws and is row tile rank*per_slab + v/ws), number
+  // their work items (a pair tile: upper half first) and serve every num_ctas-th of them. The walk
+  // is incremental — no per-tile divisions: an earlier version that called tile_coords for every
+  // tile spent more time finding its next item than reducing it.
   __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
-    const int total = p.tiles_r * p.tiles_c;
-    const int rows_per_tile = half < 0 ? kBM : 2 * kBM;
     const unsigned halves = half < 0 ? 1u : 2u;
     const unsigned me = half < 0 ? worker : 2u * worker + (unsigned)half;
     const unsigned num_ctas = num_workers * halves;
     const unsigned subs = (unsigned)(kBM / p.rs_sub_rows);
     const unsigned per_tile = halves * subs;
-    unsigned base = 0;                         // number of the first work item of the current own tile
+    const int per_slab = p.tiles_r / p.ws;             // row tiles (of this kernel's tile height) per slab
+    unsigned need = me % num_ctas;                      // first item of the current own tile that is mine: (me - base) mod num_ctas
     int served = 0;
-    for (int t = 0; t < total; ++t) {
-      int trv, tc;
-      tile_coords(p, t, trv, tc);
-      if ((trv * rows_per_tile) / p.slab_rows != p.rank) continue;
-      for (unsigned k = (me + num_ctas - base % num_ctas) % num_ctas; k < per_tile; k += num_ctas) {
-        const int tr = half < 0 ? trv : 2 * trv + (int)(k / subs);
-        if (tr * kBM >= p.rows_r) continue;
-        if (!reduce_item(p, tr, tc, (int)(k % subs), tid, served++)) return;
+    for (int first = 0; first < p.tiles_r; first += p.group_r) {
+      const int gend = min(first + p.group_r, p.tiles_r);
+      int v0 = first + (p.rank - first % p.ws + p.ws) % p.ws;       // first virtual row of this group owned by this rank
+      for (int tc = 0; tc < p.tiles_c; ++tc) {
+        for (int v = v0; v < gend; v += p.ws) {
+          const int trv = p.rank * per_slab + v / p.ws;
+          for (unsigned k = need; k < per_tile; k += num_ctas) {
+            const int tr = half < 0 ? trv : 2 * trv + (int)(k / subs);
+            if (tr * kBM < p.rows_r && !reduce_item(p, tr, tc, (int)(k % subs), tid, served++)) return;
+          }
+          // the next own tile's items start per_tile later: need = (need - per_tile) mod num_ctas
+          if (need >= per_tile) need -= per_tile;
+          else need = (need + num_ctas - per_tile % num_ctas) % num_ctas;
+        }
       }
-      base += per_tile;
     }
   }
 };
 
 // ---------------------------------------------------------------------------------------------
-// kernels: ALGO 0 push (192 threads), 1 pull / scatter (192 + 128 reducer threads)
+// kernels: ALGO 0 push (192 threads), 1 pull / scatter (192 + 192 reducer threads)
 // ---------------------------------------------------------------------------------------------
 template <int ALGO>
 __device__ __forceinline__ void rs_body(const GemmParams& p, unsigned bid, unsigned nb) {

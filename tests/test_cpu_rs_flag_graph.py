@@ -104,19 +104,23 @@ def simulate_pull(M, N, ws, ctas, pair):
     starved = wrong = 0
     for r in range(ws):
         served = {}
-        for me in range(num_ctas):                        # the arithmetic of the reducer warps' loop
-            base = 0
-            for (tr, tc) in orders[r]:
-                if tr // slab_tiles != r:
-                    continue
-                k = (me + num_ctas - base % num_ctas) % num_ctas
-                while k < per_tile:
-                    item = (tr * halves + k // SUBS, tc, k % SUBS)
-                    served[item] = served.get(item, 0) + 1
-                    if flags.get((r, item[:2]), 0) != ws:
-                        starved += 1
-                    k += num_ctas
-                base += per_tile
+        for me in range(num_ctas):                        # the reducer warps' incremental walk, restated
+            need = me % num_ctas
+            tiles_r, tiles_c, group_r = plans[r]["tiles_r"], plans[r]["tiles_c"], plans[r]["group_r"]
+            for first in range(0, tiles_r, group_r):
+                gend = min(first + group_r, tiles_r)
+                v0 = first + (r - first % ws + ws) % ws
+                for tc in range(tiles_c):
+                    for v in range(v0, gend, ws):
+                        tr = r * slab_tiles + v // ws
+                        k = need
+                        while k < per_tile:
+                            item = (tr * halves + k // SUBS, tc, k % SUBS)
+                            served[item] = served.get(item, 0) + 1
+                            if flags.get((r, item[:2]), 0) != ws:
+                                starved += 1
+                            k += num_ctas
+                        need = need - per_tile if need >= per_tile else (need + num_ctas - per_tile % num_ctas) % num_ctas
         own_tiles = [t for t in orders[r] if t[0] // slab_tiles == r]
         expect = {(tr * halves + h, tc, j) for (tr, tc) in own_tiles for h in range(halves) for j in range(SUBS)}
         wrong += len(expect.symmetric_difference(served.keys())) + sum(1 for v in served.values() if v != 1)
