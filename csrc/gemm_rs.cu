@@ -130,16 +130,16 @@ struct RsPullHooks : HookDefaults {
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
     if (p.rs_algo == 2) {
       const int owner = (tr * kBM) / p.slab_rows;
-      char* base = (char*)p.bufs[owner] + p.stage_off + (size_t)p.rank * slab_bytes(p);
+      char* base = (char*)p.peer_buf[owner] + p.stage_off + (size_t)p.rank * slab_bytes(p);
       return TileDest{base, (long long)p.rows_c, tr * kBM - owner * p.slab_rows, tc * bn, p.slab_rows, p.rows_c,
                       p.use_tma_store ? &p.tmap_out[owner] : nullptr};
     }
-    char* base = (char*)p.bufs[p.rank] + p.stage_off;
+    char* base = (char*)p.peer_buf[p.rank] + p.stage_off;
     return TileDest{base, (long long)p.rows_c, tr * kBM, tc * bn, p.rows_r, p.rows_c, p.use_tma_store ? &p.tmap_out[0] : nullptr};
   }
   // arrival counter of 128-row tile `tr`, column tile `tc` in its owner's signal pad
   __device__ __forceinline__ uint32_t* counter(const GemmParams& p, int owner, int tr, int tc) const {
-    return p.pads[owner] + p.flag_base + (size_t)(tr - owner * (p.slab_rows / kBM)) * p.tiles_c + tc;
+    return p.peer_pad[owner] + p.flag_base + (size_t)(tr - owner * (p.slab_rows / kBM)) * p.tiles_c + tc;
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
     if (tr * kBM >= p.rows_r) return true;
@@ -154,8 +154,8 @@ struct RsPullHooks : HookDefaults {
   }
   // Where rank s's partial sums of this rank's slab start.
   __device__ __forceinline__ const char* source_slab(const GemmParams& p, int s) const {
-    if (p.rs_algo == 2) return (const char*)p.bufs[p.rank] + p.stage_off + (size_t)s * slab_bytes(p);
-    return (const char*)p.bufs[s] + p.stage_off + (size_t)p.rank * slab_bytes(p);
+    if (p.rs_algo == 2) return (const char*)p.peer_buf[p.rank] + p.stage_off + (size_t)s * slab_bytes(p);
+    return (const char*)p.peer_buf[s] + p.stage_off + (size_t)p.rank * slab_bytes(p);
   }
 
   // Sum with plain loads: B vectors per thread, all W >= ws ranks' loads of all of them in flight
@@ -164,6 +164,9 @@ struct RsPullHooks : HookDefaults {
   // the same bits).
   template <int B, int W>
   __device__ __forceinline__ void reduce_loads(const GemmParams& p, int tid, int total, int vpr, int lrow0, int col0) {
+    const char* src[W];
+#pragma unroll
+    for (int s = 0; s < W; ++s) src[s] = s < p.ws ? source_slab(p, s) : nullptr;
     for (int i0 = tid; i0 < total; i0 += kRsReducerThreads * B) {
       U4 x[B][W];
 #pragma unroll
@@ -174,7 +177,7 @@ struct RsPullHooks : HookDefaults {
           const size_t off = ((size_t)(lrow0 + r) * p.rows_c + col0 + v * 8) * 2;
 #pragma unroll
           for (int s = 0; s < W; ++s)
-            if (s < p.ws) x[k][s] = ld16(source_slab(p, s) + off);
+            if (s < p.ws) x[k][s] = ld16(src[s] + off);
         }
       }
 #pragma unroll
@@ -215,7 +218,7 @@ struct RsPullHooks : HookDefaults {
     const int rows = min(p.rs_sub_rows, p.slab_rows - lrow0);
     const int total = rows * vpr;
     if (!kr_in_bounds(lrow0 >= 0 && rows > 0 && lrow0 + rows <= p.slab_rows && col0 >= 0 && col0 + vpr * 8 <= N &&
-                          (f - (p.pads[p.rank] + p.flag_base)) < (long long)p.rs_done_off, p.sync, 71))
+                          (f - (p.peer_pad[p.rank] + p.flag_base)) < (long long)p.rs_done_off, p.sync, 71))
       return false;
     if (p.mc_ptr != nullptr) {
       // in-switch sum (pull only)
@@ -258,36 +261,42 @@ struct RsPullHooks : HookDefaults {
     return true;
   }
 
-  // Reducer warps: walk the OWN tiles of the interleaved tile order in order (same sequence as
-  // tile_coords with pivot 0: row groups, inside a group column by column, inside a column the
-  // group's rows; virtual row v belongs to rank v % ws and is row tile rank*per_slab + v/ws), number
-  // their work items (a pair tile: upper half first) and serve every num_ctas-th of them. The walk
-  // is incremental — no per-tile divisions: an earlier version that called tile_coords for every
-  // tile spent more time finding its next item than reducing it.
+  // Reducer warps. The work items of the own slab are numbered in the order their tiles are
+  // computed (tile_coords with pivot 0: row groups; inside a group column by column; inside a column
+  // the group's rows; virtual row v belongs to rank v % ws and is row tile rank*per_slab + v/ws; a
+  // pair tile: upper half first) and this CTA serves items me, me + num_ctas, ... . Item number ->
+  // tile costs one division: earlier versions that walked the tile order tile by tile (a serial
+  // integer chain on one warp) spent longer finding the next item than reducing it.
   __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
     const unsigned halves = half < 0 ? 1u : 2u;
     const unsigned me = half < 0 ? worker : 2u * worker + (unsigned)half;
     const unsigned num_ctas = num_workers * halves;
-    const unsigned subs = (unsigned)(kBM / p.rs_sub_rows);
-    const unsigned per_tile = halves * subs;
-    const int per_slab = p.tiles_r / p.ws;             // row tiles (of this kernel's tile height) per slab
-    unsigned need = me % num_ctas;                      // first item of the current own tile that is mine: (me - base) mod num_ctas
+    const unsigned subs = (unsigned)(kBM / p.rs_sub_rows);           // 1, 2, 4 or 8
+    const unsigned per_tile = halves * subs;                          // a power of two
+    const unsigned tile_shift = (unsigned)__ffs((int)per_tile) - 1u;
+    const unsigned sub_shift = (unsigned)__ffs((int)subs) - 1u;
+    const int per_slab = p.tiles_r / p.ws;                            // row tiles (of this kernel's tile height) per slab
+    const unsigned total_items = ((unsigned)per_slab * (unsigned)p.tiles_c) << tile_shift;
+    // current row group: [first, gend), its own rows v0, v0 + ws, ... (n_g of them), ordinal of its first own tile
+    int first = 0, gend = min(p.group_r, p.tiles_r);
+    int v0 = (p.rank % p.ws);
+    int n_g = v0 < gend ? (gend - 1 - v0) / p.ws + 1 : 0;
+    unsigned o_base = 0;
     int served = 0;
-    for (int first = 0; first < p.tiles_r; first += p.group_r) {
-      const int gend = min(first + p.group_r, p.tiles_r);
-      int v0 = first + (p.rank - first % p.ws + p.ws) % p.ws;       // first virtual row of this group owned by this rank
-      for (int tc = 0; tc < p.tiles_c; ++tc) {
-        for (int v = v0; v < gend; v += p.ws) {
-          const int trv = p.rank * per_slab + v / p.ws;
-          for (unsigned k = need; k < per_tile; k += num_ctas) {
-            const int tr = half < 0 ? trv : 2 * trv + (int)(k / subs);
-            if (tr * kBM < p.rows_r && !reduce_item(p, tr, tc, (int)(k % subs), tid, served++)) return;
-          }
-          // the next own tile's items start per_tile later: need = (need - per_tile) mod num_ctas
-          if (need >= per_tile) need -= per_tile;
-          else need = (need + num_ctas - per_tile % num_ctas) % num_ctas;
-        }
+    for (unsigned id = me; id < total_items; id += num_ctas) {
+      const unsigned o = id >> tile_shift, k = id & (per_tile - 1u);
+      while (o >= o_base + (unsigned)(n_g * p.tiles_c)) {             // advance to the group that holds tile o
+        o_base += (unsigned)(n_g * p.tiles_c);
+        first += p.group_r;
+        gend = min(first + p.group_r, p.tiles_r);
+        v0 = first + (p.rank - first % p.ws + p.ws) % p.ws;
+        n_g = v0 < gend ? (gend - 1 - v0) / p.ws + 1 : 0;
       }
+      const int idx = (int)(o - o_base);
+      const int tc = idx / n_g, j = idx - tc * n_g;
+      const int trv = p.rank * per_slab + v0 / p.ws + j;              // (v0 + j*ws) / ws
+      const int tr = half < 0 ? trv : 2 * trv + (int)(k >> sub_shift);
+      if (tr * kBM < p.rows_r && !reduce_item(p, tr, tc, (int)(k & (subs - 1u)), tid, served++)) return;
     }
   }
 };
@@ -430,12 +439,13 @@ KR_API int kr_rs_plan(int M, int N, int ws, int rank, int algo, int num_ctas, in
 
 // Fused GEMM -> reduce-scatter. a[M, K_local], bt[N, K_local]; out[M/ws, N] bf16.
 // bufs[r] = rank r's staging workspace (bufs: device table; bufs_host: the same addresses in host
-// memory, used to describe staging to TMA, or nullptr): push needs M*N*2 bytes, pull and scatter
+// memory, used to describe staging to TMA, or nullptr; pads_host likewise for the signal pads): push needs M*N*2 bytes, pull and scatter
 // 2*M*N*2 (two halves, alternating with call_parity) and DEDICATED to this op. mc_ptr: multicast
 // address of the staging workspace (pull then sums in the NVSwitch) or nullptr (peer loads).
 // algo: 0 push, 1 pull, 2 scatter. Tile counters live in the signal pads from word flag_base on
 // (zero on entry, zero again after the call); pull and scatter use the bank selected by call_parity.
-KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads, void* mc_ptr, int rank,
+KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* const* pads,
+                           uint32_t* const* pads_host, void* mc_ptr, int rank,
                            int ws, const void* a, long long lda, const void* bt, long long ldb, void* out,
                            long long ldo, int M, int N, int K, int algo, int call_parity, uint32_t pad_base,
                            uint32_t flag_base, unsigned long long pad_words, unsigned long long staging_bytes,
@@ -482,6 +492,12 @@ KR_API int kr_gemm_rs_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
       p.use_tma_store = ok ? 1 : 0;
     }
   } else {
+    KR_REQUIRE(bufs_host != nullptr && pads_host != nullptr && ws <= 8,
+               "pull and scatter need the peers' addresses on the host and world sizes up to 8");
+    for (int r = 0; r < ws; ++r) {
+      p.peer_buf[r] = bufs_host[r];
+      p.peer_pad[r] = pads_host[r];
+    }
     const unsigned long long half = staging_bytes / 2 / 1024 * 1024;
     KR_REQUIRE(half >= mn2, "staging workspace too small (pull and scatter need 2 * M * N * 2 bytes)");
     KR_REQUIRE(pad_words > flag_base, "signal pad too small for the tile counters");

@@ -72,6 +72,10 @@ struct alignas(64) GemmParams {
   int rank, ws;
   void* const* bufs;         // [ws] symmetric workspaces (RS/AR staging, AG shards)
   uint32_t* const* pads;     // [ws] signal pads
+  // The same addresses by value (world sizes up to 8, filled by launchers that know them on the
+  // host): read from the kernel's parameter space instead of through two dependent global loads.
+  void* peer_buf[8];
+  uint32_t* peer_pad[8];
   uint32_t pad_base;         // first barrier slot
   uint32_t flag_base;        // first tile-flag word in the signal pad (RS / AR)
   // AG

@@ -305,7 +305,10 @@ def gemm_reduce_scatter(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Ten
             hdl = symm_mem.get_symm_mem_workspace(group, M * N * 2, a.device)
             calls = 0
         mc = hdl.multicast_ptr if (algo == "pull" and config.rs_nvls()) else 0
-        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev,
+        pads_host = getattr(hdl, "_host_pad_array", None)
+        if pads_host is None:
+            pads_host = hdl._host_pad_array = (ctypes.c_void_p * ws)(*hdl.signal_pad_ptrs)
+        _lib.check(L.kr_gemm_rs_bf16(hdl.buffer_ptrs_dev, hdl._host_ptr_array, hdl.signal_pad_ptrs_dev, pads_host,
                                      mc or None, hdl.rank, ws, a2.data_ptr(), lda, bt.data_ptr(), ldb,
                                      out.data_ptr(), N, M, N, K, {"push": 0, "pull": 1, "scatter": 2}[algo], calls & 1, 0,
                                      config.TILE_FLAG_BASE, hdl.signal_pad_words, hdl.buffer_size, s))

@@ -97,7 +97,7 @@ _PROTOS = {
                              c_int, c_int, c_int, _P]),
     "kr_ag_gemm_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int,
                                 c_int, _P, _P, c_int, c_uint32, c_int, c_ulonglong, c_uint32, c_ulonglong, c_int, _P]),
-    "kr_gemm_rs_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
+    "kr_gemm_rs_bf16": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
                                 c_int, c_int, c_int, c_uint32, c_uint32, c_ulonglong, c_ulonglong, _P]),
     "kr_gemm_rs_set_trace": (c_int, [_P, c_ulonglong]),
     "kr_rs_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),

@@ -83,7 +83,8 @@ def simulate_push(M, N, ws, ctas, pair, flush_before_wait):
 
 def simulate_pull(M, N, ws, ctas, pair):
     """Pull and scatter share this protocol. Returns (work items whose tile never got all ws
-    signals, work items served by no CTA or by more than one)."""
+    signals, work items served by no CTA or by more than one). Also checks that every CTA meets its
+    items in the order their tiles are computed (no item waits behind a later tile's)."""
     plans = [_plan(M, N, ws, r, 1, ctas, pair) for r in range(ws)]
     orders = [_order(pl) for pl in plans]
     assert all(o == orders[0] for o in orders)            # every rank walks the same order
@@ -102,25 +103,35 @@ def simulate_pull(M, N, ws, ctas, pair):
                 key = (tr // slab_tiles, (tr * halves + h, tc))
                 flags[key] = flags.get(key, 0) + 1
     starved = wrong = 0
+    order_pos = {t: i for i, t in enumerate(orders[0])}
     for r in range(ws):
         served = {}
-        for me in range(num_ctas):                        # the reducer warps' incremental walk, restated
-            need = me % num_ctas
-            tiles_r, tiles_c, group_r = plans[r]["tiles_r"], plans[r]["tiles_c"], plans[r]["group_r"]
-            for first in range(0, tiles_r, group_r):
-                gend = min(first + group_r, tiles_r)
-                v0 = first + (r - first % ws + ws) % ws
-                for tc in range(tiles_c):
-                    for v in range(v0, gend, ws):
-                        tr = r * slab_tiles + v // ws
-                        k = need
-                        while k < per_tile:
-                            item = (tr * halves + k // SUBS, tc, k % SUBS)
-                            served[item] = served.get(item, 0) + 1
-                            if flags.get((r, item[:2]), 0) != ws:
-                                starved += 1
-                            k += num_ctas
-                        need = need - per_tile if need >= per_tile else (need + num_ctas - per_tile % num_ctas) % num_ctas
+        last_pos = {}
+        tiles_r, tiles_c, group_r = plans[r]["tiles_r"], plans[r]["tiles_c"], plans[r]["group_r"]
+        total_items = slab_tiles * tiles_c * per_tile
+        for me in range(num_ctas):                        # the reducer warps' item -> tile arithmetic, restated
+            first, gend = 0, min(group_r, tiles_r)
+            v0 = r % ws
+            n_g = (gend - 1 - v0) // ws + 1 if v0 < gend else 0
+            o_base = 0
+            for item_id in range(me, total_items, num_ctas):
+                o, k = item_id // per_tile, item_id % per_tile
+                while o >= o_base + n_g * tiles_c:
+                    o_base += n_g * tiles_c
+                    first += group_r
+                    gend = min(first + group_r, tiles_r)
+                    v0 = first + (r - first % ws + ws) % ws
+                    n_g = (gend - 1 - v0) // ws + 1 if v0 < gend else 0
+                idx = o - o_base
+                tc = idx // n_g
+                tr = r * slab_tiles + v0 // ws + (idx - tc * n_g)
+                item = (tr * halves + k // SUBS, tc, k % SUBS)
+                served[item] = served.get(item, 0) + 1
+                if flags.get((r, item[:2]), 0) != ws:
+                    starved += 1
+                pos = order_pos[(item[0] // halves, item[1])]
+                assert pos >= last_pos.get(me, -1), "items must follow the tile order"
+                last_pos[me] = pos
         own_tiles = [t for t in orders[r] if t[0] // slab_tiles == r]
         expect = {(tr * halves + h, tc, j) for (tr, tc) in own_tiles for h in range(halves) for j in range(SUBS)}
         wrong += len(expect.symmetric_difference(served.keys())) + sum(1 for v in served.values() if v != 1)

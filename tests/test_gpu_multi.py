@@ -158,6 +158,16 @@ def _all_ops(rank, ws):
                 torch.cuda.synchronize()
                 assert torch.equal(ag, a_full), (backend, splits)
                 torch.testing.assert_close(c.float(), gold_c, atol=1e-1, rtol=1e-1)
+    plain_out = torch.zeros_like(a_full)                   # ordinary a_out: filled by a copy of the library's buffer
+    sym_out = symm_mem.empty(*a_full.shape, dtype=torch.bfloat16, device=dev)
+    symm_mem.rendezvous(sym_out)
+    for target in (plain_out, sym_out, plain_out):
+        target.zero_()
+        ag, c = fused.all_gather_matmul(a_sh, bt.t(), a_out=target, backend="push")
+        torch.cuda.synchronize()
+        assert ag.data_ptr() == target.data_ptr() and torch.equal(ag, a_full)
+        torch.testing.assert_close(c.float(), gold_c, atol=1e-1, rtol=1e-1)
+    dist.barrier()
     # -- GEMM + reduce-scatter: both exchange algorithms and the copy-engine variant
     #    (reference: test/test_gemm_reduce_scatter.py); the second shape gives every CTA pair
     #    several 256 x 256 tiles (the tensor-parallel MLP's M = 2048, N = 8192)
