@@ -236,6 +236,92 @@ __device__ __forceinline__ void ag_push_cta(const GemmParams& p, unsigned comm_i
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// AG multicast push engine: every rank writes its own shard ONCE, to the multicast address of the
+// gathered buffer; the NVSwitch delivers it to all ranks (this one included). One elected thread
+// streams the shard local memory -> shared memory with bulk loads; all threads of the comm CTA
+// forward each landed piece with multimem.st (posted, from registers, so shared memory only holds
+// data on its way in). A finished chunk's flag is raised on every rank with one multimem.red.
+// NVLink bytes out per rank: one shard instead of ws - 1 of them.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ag_mc_cta(const GemmParams& p, unsigned comm_id, unsigned n_comm,
+                                          unsigned char* smem_raw) {
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + kAgSlots * kAgPiece;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAgSlots; ++s) mbar_init(bars + 8u * s, 1);
+    mbar_fence_init();
+  }
+  if (p.ag_entry_barrier && !symm_mem_sync<true, true>(p.pads, p.pad_base / p.ws + comm_id, p.rank, p.ws, p.sync, 52)) return;
+  __syncthreads();
+  const size_t row_bytes = (size_t)p.K * 2;
+  const size_t chunk_bytes = (size_t)p.chunk_rows * row_bytes;
+  const size_t pieces = (chunk_bytes + kAgPiece - 1) / kAgPiece;            // per chunk
+  const size_t mine_per_chunk = pieces > comm_id ? (pieces - comm_id + n_comm - 1) / n_comm : 0;
+  const size_t total_mine = mine_per_chunk * (size_t)p.splits;
+  const char* shard = (const char*)p.ag_shard;
+  char* mc_out = (char*)p.ag_mc_out + (size_t)p.rank * p.splits * chunk_bytes;   // this rank's rows in every gathered buffer
+  // j-th piece of this CTA: chunk j / mine_per_chunk, piece comm_id + (j % mine_per_chunk) * n_comm
+  auto piece_off = [&](size_t j, uint32_t& bytes) -> size_t {
+    const size_t sp = j / mine_per_chunk, pc = comm_id + (j - sp * mine_per_chunk) * n_comm;
+    const size_t off = pc * kAgPiece;
+    bytes = (uint32_t)min((size_t)kAgPiece, chunk_bytes - off);
+    return sp * chunk_bytes + off;
+  };
+  if (threadIdx.x == 0) {
+    for (size_t j = 0; j < total_mine && j < (size_t)kAgSlots; ++j) {
+      uint32_t bytes;
+      const size_t off = piece_off(j, bytes);
+      mbar_expect_tx(bars + 8u * (uint32_t)j, bytes);
+      bulk_load_1d(base + (uint32_t)j * kAgPiece, shard + off, bytes, bars + 8u * (uint32_t)j);
+    }
+  }
+  bool ok = true;
+  for (size_t j = 0; j < total_mine; ++j) {
+    const uint32_t slot = (uint32_t)(j % kAgSlots);
+    uint32_t bytes;
+    const size_t off = piece_off(j, bytes);
+    ok = mbar_wait(bars + 8u * slot, (uint32_t)(j / kAgSlots) & 1u, p.sync, 53);
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) break;
+    const unsigned char* src = base_ptr + (size_t)slot * kAgPiece;
+    for (uint32_t v = threadIdx.x; v < bytes / 16; v += blockDim.x)
+      multimem_st16(mc_out + off + (size_t)v * 16, *(const U4*)(src + (size_t)v * 16));
+    __syncthreads();                                   // every thread has read the slot and issued its stores
+    if (threadIdx.x == 0) {
+      const size_t jn = j + kAgSlots;
+      if (jn < total_mine) {
+        uint32_t nbytes;
+        const size_t noff = piece_off(jn, nbytes);
+        fence_proxy_async();                           // the slot's generic reads before the bulk copy overwrites it
+        mbar_expect_tx(bars + 8u * slot, nbytes);
+        bulk_load_1d(base + slot * kAgPiece, shard + noff, nbytes, bars + 8u * slot);
+      }
+      // last of my pieces of this chunk: count myself in; the comm CTA that completes the chunk
+      // raises its flag on every rank
+      if ((j + 1) % mine_per_chunk == 0) {
+        const int sp = (int)(j / mine_per_chunk);
+        uint32_t* cnt = p.counters + (size_t)p.rank * p.splits + sp;
+        const uint32_t old = atom_add_acqrel_gpu(cnt, 1u);
+        if (old == n_comm - 1) {
+          *cnt = 0;
+          multimem_red_add_release_u32(p.ag_mc_flags + p.rank * p.splits + sp, 1u);
+        }
+      }
+    }
+  }
+  // the caller's progress words: in the order the chunks become usable here
+  if (threadIdx.x == 0 && comm_id == 0 && p.progress != nullptr && ok) {
+    for (int sp = 0; sp < p.splits && ok; ++sp)
+      for (int step = 0; step < p.ws && ok; ++step) {
+        const int idx = ((p.rank + step) % p.ws) * p.splits + sp;
+        ok = wait_flag_acquire_sys(p.pads[p.rank] + p.flag_base + idx, 1u, p.sync, 54);
+        if (ok) st_release_gpu(p.progress + idx, 1u);
+      }
+  }
+}
+
 // Push mode, every CTA on its way out: the last one puts this call's flag bank back to zero (all
 // peers have signalled — every consumer has seen every flag — and the peers' next signals to this
 // bank belong to the call after next).
@@ -265,7 +351,8 @@ __device__ __forceinline__ void gemm_body(const GemmParams& p, unsigned bid, uns
     gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
-      if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      if (p.ag_push && p.ag_mc_out != nullptr) ag_mc_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      else if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
       else ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
       AgHooks h;
@@ -290,7 +377,8 @@ __device__ __forceinline__ void gemm_pair_body(const GemmParams& p, unsigned bid
     gemm_mainloop_pair(p, bid / 2, nb / 2, h, smem_raw);
   } else if (p.mode == GEMM_AG) {
     if (bid >= n_mma) {
-      if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      if (p.ag_push && p.ag_mc_out != nullptr) ag_mc_cta(p, bid - n_mma, nb - n_mma, smem_raw);
+      else if (p.ag_push) ag_push_cta(p, bid - n_mma, nb - n_mma, smem_raw);
       else ag_comm_cta(p, bid - n_mma, nb - n_mma, smem_raw);
     } else {
       AgHooks h;
@@ -578,11 +666,16 @@ KR_API int kr_gemm_bf16(const void* a, long long lda, const void* bt, long long 
 //              rank's buffer and raise flags in the signal pads from word flag_base on (zero on entry,
 //              zero again after the call; the caller alternates two banks). entry_barrier: wait for
 //              all ranks before the first remote write (needed unless the caller alternates buffers).
+//              mc_out / mc_flags: multicast addresses of the gathered buffer (at a_out_off) and of the
+//              flag word flag_base — then the shard is written once, through the NVSwitch, and the
+//              tile order after the own shard goes chunk by chunk over all peers; nullptr: one
+//              unicast copy per peer, the peer that needs the shard first served first.
 KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void* own_shard, int rank, int ws,
                            void* a_out, const void* bt, long long ldb, void* c, long long ldc, int shard_rows, int N,
                            int K, int splits, uint32_t* progress, uint32_t* counters, int num_comm_ctas,
                            uint32_t pad_base, int push, unsigned long long a_out_off, uint32_t flag_base,
-                           unsigned long long pad_words, int entry_barrier, cudaStream_t stream) {
+                           unsigned long long pad_words, int entry_barrier, void* mc_out, uint32_t* mc_flags,
+                           cudaStream_t stream) {
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
@@ -625,6 +718,11 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
     KR_REQUIRE(!entry_barrier || (unsigned long long)pad_base + (unsigned long long)d->num_sms * ws <= flag_base,
                "barrier slots overlap chunk flags");
     p.flag_base = flag_base;
+    if (mc_out != nullptr) {
+      KR_REQUIRE(mc_flags != nullptr, "multicast push needs the multicast address of the flags");
+      p.ag_mc_out = mc_out;
+      p.ag_mc_flags = mc_flags;
+    }
   }
   p.pivot_r = (rank * shard_rows) / kBM;   // start on (or next to) the local shard
   if (p.tiles_r > 0) p.pivot_r %= p.tiles_r;
@@ -638,7 +736,18 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
   unsigned n_comm = num_comm_ctas > 0 ? (unsigned)num_comm_ctas : (num_comm_ctas < 0 ? 0u : 8u);
   if (n_comm >= cap) n_comm = cap > 1 ? cap / 2 : 1;
   KR_REQUIRE(cap >= 2, "all-gather GEMM needs at least two CTAs");
-  if (pair_eligible(bn, p) && cap >= 4) return launch_pair(p, cap, n_comm, stream);
+  const bool pair = pair_eligible(bn, p) && cap >= 4;
+  if (p.ag_mc_out != nullptr && ws > 1) {
+    // chunk-major order needs chunks made of whole row tiles of the kernel that runs
+    const int tile_rows = pair ? 256 : kBM;
+    if (p.chunk_rows % tile_rows == 0) {
+      p.ag_chunk_major = p.chunk_rows / tile_rows;
+      p.ag_tiles_per_shard = shard_rows / tile_rows;
+      p.pivot_r = 0;
+      p.group_r = p.ag_chunk_major * (pair ? 2 : 1);       // launch_pair halves it again
+    }
+  }
+  if (pair) return launch_pair(p, cap, n_comm, stream);
   unsigned n_mma = (unsigned)(p.tiles_r * p.tiles_c);
   if (n_mma > cap - n_comm) n_mma = cap - n_comm;
   p.num_mma_ctas = (int)n_mma;
@@ -697,5 +806,23 @@ KR_API int kr_tile_order(int tiles_r, int tiles_c, int group_r, int pivot_r, int
   p.pivot_r = pivot_r;
   p.interleave_r = interleave_r;
   for (int t = 0; t < tiles_r * tiles_c; ++t) tile_coords(p, t, out[2 * t], out[2 * t + 1]);
+  return KR_SUCCESS;
+}
+
+// The same for the chunk-major order of the all-gather GEMM fed by a multicast push: `tiles_per_shard`
+// row tiles per rank, `chunk_tiles` of them per chunk.
+KR_API int kr_tile_order_ag(int tiles_c, int group_r, int rank, int ws, int tiles_per_shard, int chunk_tiles, int* out) {
+  KR_REQUIRE(tiles_c >= 1 && group_r >= 1 && ws >= 1 && rank >= 0 && rank < ws, "bad tiling");
+  KR_REQUIRE(chunk_tiles >= 1 && tiles_per_shard % chunk_tiles == 0, "chunks must be whole row tiles");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_r = ws * tiles_per_shard;
+  p.tiles_c = tiles_c;
+  p.group_r = group_r;
+  p.rank = rank;
+  p.ws = ws;
+  p.ag_chunk_major = chunk_tiles;
+  p.ag_tiles_per_shard = tiles_per_shard;
+  for (int t = 0; t < p.tiles_r * tiles_c; ++t) tile_coords(p, t, out[2 * t], out[2 * t + 1]);
   return KR_SUCCESS;
 }

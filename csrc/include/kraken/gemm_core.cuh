@@ -84,6 +84,10 @@ struct alignas(64) GemmParams {
   uint32_t* counters;        // [ws * splits] arrival counters (zeroed, self-resetting)
   int splits, shard_rows, chunk_rows;
   const void* ag_shard;      // push: this rank's own shard [shard_rows, K]
+  int ag_chunk_major;        // > 0: row tiles after the own shard go chunk by chunk over all peers (tiles per chunk)
+  int ag_tiles_per_shard;    // row tiles (of this kernel's tile height) per shard, for ag_chunk_major
+  void* ag_mc_out;           // multicast address of the gathered buffer (multicast push) or nullptr
+  uint32_t* ag_mc_flags;     // multicast address of this call's chunk flags (multicast push)
   int ag_push;               // 1: every rank pushes its shard into the peers' gathered buffers (comm CTAs)
   int ag_entry_barrier;      // push into a caller-owned symmetric a_out: wait until every rank has entered
   unsigned long long ag_out_off;   // push: byte offset of the gathered buffer inside bufs[r]
@@ -124,6 +128,22 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int t,
   // Interleaved slabs: consecutive row tiles of the order belong to consecutive slabs (owners), so
   // every owner's tiles finish at an even rate instead of slab after slab.
   if (p.interleave_r > 1) tr = (tr % p.interleave_r) * (p.tiles_r / p.interleave_r) + tr / p.interleave_r;
+  // All-gather GEMM fed by a multicast push: every peer's shard arrives chunk by chunk at the same
+  // time, so after the own shard the order is chunk 0 of every peer, chunk 1 of every peer, ...
+  // (`tr` counts positions from the start of the own shard; pivot_r is not used in this mode).
+  if (p.ag_chunk_major > 0) {
+    const int T = p.ag_tiles_per_shard, C = p.ag_chunk_major;
+    if (tr < T) {
+      tr += p.rank * T;
+    } else {
+      const int j = tr - T, round = (p.ws - 1) * C;
+      const int c = j / round, r = j - c * round;
+      const int s = r / C + 1, t = r - (s - 1) * C;
+      int src = p.rank + s;
+      if (src >= p.ws) src -= p.ws;
+      tr = src * T + c * C + t;
+    }
+  }
 }
 
 // Per-tile timeline for performance work: when GemmParams::trace is set, one thread per role

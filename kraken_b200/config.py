@@ -14,6 +14,7 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``push`` (default: comm CTAs write the own shard into
                             the peers' gathered buffers), ``ce`` (copy engines + stream flags) or ``sm`` (comm CTAs
                             pull the peers' shards)
+``KRAKEN_AG_MC``            ``0``: the push engine writes peer by peer even when a multicast mapping exists
 ``KRAKEN_RS_ALGO``          ``pull`` (reducer warps sum the ranks' staged tiles with peer loads), ``scatter`` (tiles are
                             stored into the owner's staging, reducer warps sum local memory) or ``push`` (tiles
                             are stored into the owner's staging and summed in its epilogue)
@@ -68,6 +69,12 @@ def num_comm_sms() -> int:
 def ag_mode() -> str:
     v = os.environ.get("KRAKEN_AG_MODE", "push").strip().lower()
     return v if v in ("push", "sm", "ce") else "push"
+
+
+def ag_multicast() -> bool:
+    """Whether the push engine of the all-gather GEMM writes through the NVSwitch (multimem.st) when
+    the gathered buffer has a multicast mapping (KRAKEN_AG_MC, default 1)."""
+    return os.environ.get("KRAKEN_AG_MC", "1") != "0"
 
 
 def rs_algo() -> str:

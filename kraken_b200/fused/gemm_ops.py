@@ -80,17 +80,23 @@ def _default_comm_ctas(n_local: int, ws: int) -> int:
     return max(2, min(32, n))
 
 
-def _default_push_ctas(shard_bytes: int, ws: int, flops: float) -> int:
-    """Comm CTAs of the PUSH engine: each rank writes ws copies of its shard (ws - 1 over NVLink)
-    during the GEMM; a comm CTA streams local memory -> shared memory -> peer with posted bulk
-    stores, taken as 60 GB/s. KRAKEN_NUM_COMM_SMS overrides."""
+def _default_push_ctas(shard_bytes: int, ws: int, flops: float, multicast: bool) -> int:
+    """Comm CTAs of the PUSH engine. Unicast: each rank writes ws copies of its shard during the GEMM
+    and a comm CTA (local memory -> shared memory -> peer, bounded by what its shared memory keeps
+    in flight) was measured at about 20 GB/s. Multicast: one copy, forwarded from registers, taken
+    as 40 GB/s per comm CTA; it should be done in about half the GEMM's time, since every peer's
+    shard arrives at the same pace. KRAKEN_NUM_COMM_SMS overrides."""
     import os
 
     if "KRAKEN_NUM_COMM_SMS" in os.environ:
         return config.num_comm_sms()
     t_gemm = flops / 1.45e15
-    rate = ws * shard_bytes / max(t_gemm, 1e-6)
-    n = int(-(-rate // 60e9))
+    if multicast:
+        rate = shard_bytes / max(0.5 * t_gemm, 1e-6)
+        n = int(-(-rate // 40e9))
+    else:
+        rate = ws * shard_bytes / max(t_gemm, 1e-6)
+        n = int(-(-rate // 20e9))
     n = (n + 1) & ~1
     return max(2, min(16, n))
 
@@ -104,9 +110,12 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     symmetric memory. The persistent tcgen05 GEMM starts on the local shard (rank pivot) and
     consumes remote chunks as their flags appear. Engines that move the shards (kwarg ``backend``):
 
-    * ``"push"`` (default): comm CTAs of the same launch write this rank's shard into every peer's
-      gathered buffer with posted bulk stores — first to the rank that needs it first — and raise
-      the chunk's flag in that peer's signal pad. One launch, no barrier, no second stream. The
+    * ``"push"`` (default): comm CTAs of the same launch write this rank's shard into every rank's
+      gathered buffer and raise the chunk's flag in the signal pads: once, through the NVSwitch
+      (``multimem.st`` / ``multimem.red``), when the gathered buffer has a multicast mapping — the
+      tile order after the own shard then goes chunk by chunk over all peers, as the data arrives —
+      else peer by peer with posted bulk stores, the rank that needs the shard first served first
+      (``multicast=False`` forces this form). One launch, no barrier, no second stream. The
       gathered buffer must be symmetric: with ``a_out=None`` the op returns a view of a
       double-buffered library workspace, valid until the second next call on the same group; a
       symmetric ``a_out`` is written in place (at the price of an entry barrier); an ordinary
@@ -174,12 +183,17 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
         if off is None:
             off = (calls & 1) * half
             gathered = oh.get_buffer(rank, (M, K), torch.bfloat16, storage_offset=off // 2)
-        n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_push_ctas(shard_rows * K * 2, ws, 2.0 * M * N * K)
+        flag_base = config.TILE_FLAG_BASE + (calls & 1) * _AG_FLAG_BANK
+        use_mc = bool(oh.multicast_ptr) and bool(kwargs.get("multicast", config.ag_multicast()))
+        if use_mc and progress is None and "splits_per_rank" not in kwargs and shard_rows % 1024 == 0:
+            splits = 4                      # all shards arrive at the same pace: finer chunks let the GEMM start sooner
+        mc_out = oh.multicast_ptr + off if use_mc else None
+        mc_flags = oh.multicast_ptr + oh.buffer_size + 4 * flag_base if use_mc else None
+        n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_push_ctas(shard_rows * K * 2, ws, 2.0 * M * N * K, use_mc)
         _lib.check(L.kr_ag_gemm_bf16(oh.buffer_ptrs_dev, oh.signal_pad_ptrs_dev, a_shared.data_ptr(), rank, ws,
                                      gathered.data_ptr(), bt.data_ptr(), ldb, c.data_ptr(), N, shard_rows, N, K, splits,
                                      progress.data_ptr() if progress is not None else None, counters.data_ptr(), n_comm,
-                                     0, 1, off, config.TILE_FLAG_BASE + (calls & 1) * _AG_FLAG_BANK, oh.signal_pad_words,
-                                     barrier, stream))
+                                     0, 1, off, flag_base, oh.signal_pad_words, barrier, mc_out, mc_flags, stream))
         if user_out is not None:
             user_out.copy_(gathered)
             gathered = user_out
@@ -189,7 +203,7 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
         a_out = torch.empty((M, K), dtype=a_shared.dtype, device=dev)
     if progress is None:
         progress = torch.zeros(ws * splits, dtype=torch.uint32, device=dev)
-    args_tail = (0, 0, 0, 0, 0, stream)     # pad_base, then the push arguments (unused)
+    args_tail = (0, 0, 0, 0, 0, None, None, stream)     # the push arguments (unused)
     if ws == 1 and emu is None:
         # nothing to gather: a device copy fills a_out while the GEMM reads the shard in place
         a_out.copy_(a_shared)

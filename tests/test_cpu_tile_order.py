@@ -55,3 +55,24 @@ def test_interleaved_slabs_every_tile_once_and_owners_rotate(tiles_r, tiles_c, g
     # the first `il` tiles of the order hit `il` different slabs when a group holds at least `il` rows
     if group_r >= il:
         assert {r // per_slab for r, _ in order[:il]} == set(range(il))
+
+
+@pytest.mark.parametrize("ws,rank,T,C", [(8, 3, 4, 1), (8, 0, 4, 2), (4, 3, 8, 2), (2, 1, 16, 4), (3, 2, 6, 3), (1, 0, 4, 2)])
+def test_all_gather_chunk_major_order(ws, rank, T, C):
+    # multicast push: own shard first, then chunk 0 of every peer (rank+1, rank+2, ...), chunk 1 of every peer, ...
+    tiles_c = 5
+    n = ws * T * tiles_c
+    buf = (ctypes.c_int * (2 * n))()
+    klib.check(klib.lib().kr_tile_order_ag(tiles_c, C, rank, ws, T, C, buf))
+    order = [(buf[2 * i], buf[2 * i + 1]) for i in range(n)]
+    assert sorted(order) == [(r, c) for r in range(ws * T) for c in range(tiles_c)]
+    rows = []
+    for r, _ in order:                       # row tiles in order of first appearance
+        if r not in rows:
+            rows.append(r)
+    expect = [rank * T + i for i in range(T)]
+    for c in range(T // C):
+        for s in range(1, ws):
+            src = (rank + s) % ws
+            expect += [src * T + c * C + t for t in range(C)]
+    assert rows == expect
