@@ -11,10 +11,10 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_GEMM_PAIR``        ``0`` forces the single-CTA GEMM kernel (default: CTA pairs when eligible)
 ``KRAKEN_GEMM_GROUP``       row tiles per column sweep of the GEMM tile order (default 16)
 ``KRAKEN_TMA_STORE``        ``0`` makes the GEMM epilogue use vector stores instead of TMA stores
-``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``push`` (default: comm CTAs write the own shard into
-                            the peers' gathered buffers), ``ce`` (copy engines + stream flags) or ``sm`` (comm CTAs
-                            pull the peers' shards)
-``KRAKEN_AG_MC``            ``0``: the push engine writes peer by peer even when a multicast mapping exists
+``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``auto`` (default: ``push`` at 2 ranks, ``ce`` above),
+                            ``push`` (comm CTAs write the own shard into the peers' gathered buffers), ``ce`` (copy
+                            engines + stream flags) or ``sm`` (comm CTAs pull the peers' shards)
+``KRAKEN_AG_MC``            ``1``: the push engine writes once through the NVSwitch (multimem.st) when a multicast mapping exists
 ``KRAKEN_RS_ALGO``          ``pull`` (reducer warps sum the ranks' staged tiles with peer loads), ``scatter`` (tiles are
                             stored into the owner's staging, reducer warps sum local memory) or ``push`` (tiles
                             are stored into the owner's staging and summed in its epilogue)
@@ -67,14 +67,15 @@ def num_comm_sms() -> int:
 
 
 def ag_mode() -> str:
-    v = os.environ.get("KRAKEN_AG_MODE", "push").strip().lower()
-    return v if v in ("push", "sm", "ce") else "push"
+    v = os.environ.get("KRAKEN_AG_MODE", "auto").strip().lower()
+    return v if v in ("auto", "push", "sm", "ce") else "auto"
 
 
 def ag_multicast() -> bool:
     """Whether the push engine of the all-gather GEMM writes through the NVSwitch (multimem.st) when
-    the gathered buffer has a multicast mapping (KRAKEN_AG_MC, default 1)."""
-    return os.environ.get("KRAKEN_AG_MC", "1") != "0"
+    the gathered buffer has a multicast mapping (KRAKEN_AG_MC, default 0: measured at 2 GPUs a comm CTA
+    forwards about 10 GB/s with multimem.st, half of what it reaches with bulk stores to one peer)."""
+    return os.environ.get("KRAKEN_AG_MC", "0") == "1"
 
 
 def rs_algo() -> str:

@@ -149,6 +149,11 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
         splits = 1
     dev = a_shared.device
     backend = kwargs.get("backend", config.ag_mode())
+    if backend == "auto":
+        # Measured: a comm CTA moves 10-20 GB/s (what its shared memory keeps in flight), so pushing
+        # ws copies of a shard needs 8 CTAs at 2 ranks and far too many at 8; the copy engines move the
+        # same bytes at link rate without using an SM.
+        backend = "push" if ws <= 2 else "ce"
     if backend not in ("push", "ce", "sm"):
         raise ValueError("backend must be 'push', 'ce' or 'sm'")
     emu = hdl.group.emu

@@ -151,10 +151,10 @@ def _all_ops(rank, ws):
     dist.all_gather(parts, a_sh)
     a_full = torch.cat(parts, 0)
     gold_c = a_full.float() @ bt.float().t()
-    for backend in ("push", "push_unicast", "sm", "ce"):
+    for backend in ("push_multicast", "push_unicast", "sm", "ce"):
         for splits in (1, 2, 4):
             for _ in range(3):
-                kw = {"multicast": False} if backend == "push_unicast" else {}
+                kw = {"multicast": backend == "push_multicast"} if backend.startswith("push") else {}
                 ag, c = fused.all_gather_matmul(a_sh, bt.t(), splits_per_rank=splits, backend=backend.split("_")[0], **kw)
                 torch.cuda.synchronize()
                 assert torch.equal(ag, a_full), (backend, splits)
