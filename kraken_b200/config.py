@@ -15,9 +15,9 @@ kraken/comm/two_shot_all_reduce.py:153).
                             ``push`` (comm CTAs write the own shard into the peers' gathered buffers), ``ce`` (copy
                             engines + stream flags) or ``sm`` (comm CTAs pull the peers' shards)
 ``KRAKEN_AG_MC``            ``1``: the push engine writes once through the NVSwitch (multimem.st) when a multicast mapping exists
-``KRAKEN_RS_ALGO``          ``pull`` (reducer warps sum the ranks' staged tiles with peer loads), ``scatter`` (tiles are
-                            stored into the owner's staging, reducer warps sum local memory) or ``push`` (tiles
-                            are stored into the owner's staging and summed in its epilogue)
+``KRAKEN_RS_ALGO``          ``scatter`` (default: tiles are stored into the owner's staging, reducer warps sum local
+                            memory), ``pull`` (reducer warps sum the ranks' staged tiles with peer loads) or
+                            ``push`` (tiles are stored into the owner's staging and summed in its epilogue)
 ``KRAKEN_ONE_SHOT``         ``push`` (default: small one-shot all-reduces write into the peers' workspace and meet in
                             one barrier) or ``pull`` (copy-in, barrier, remote loads, exit barrier)
 ``KRAKEN_RS_NVLS``          ``1``: the pull reduce-scatter sums with ``multimem.ld_reduce`` (default 0: peer loads)
@@ -79,8 +79,8 @@ def ag_multicast() -> bool:
 
 
 def rs_algo() -> str:
-    v = os.environ.get("KRAKEN_RS_ALGO", "pull").strip().lower()
-    return v if v in ("pull", "push", "scatter") else "pull"
+    v = os.environ.get("KRAKEN_RS_ALGO", "scatter").strip().lower()
+    return v if v in ("pull", "push", "scatter") else "scatter"
 
 
 def one_shot_mode() -> str:
