@@ -70,7 +70,6 @@ def _run(args, M, H, F) -> None:
     x_symm = x_bufs[0]
     a_out = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     progress = torch.zeros(ws, dtype=torch.uint32, device=dev)
-    result_host = torch.empty(1, dtype=torch.float32).pin_memory()
     copy_stream = torch.cuda.Stream()
     b_up = w_up_t.t()        # [H, F/ws] with b.T contiguous, as the reference requires
     b_down = w_down_t.t()
@@ -84,10 +83,17 @@ def _run(args, M, H, F) -> None:
         return kraken.fused.gemm_reduce_scatter_ce_persistent(h, b_down)
 
     def run_e2e(k):
-        # same serving loop as the library's arm: H2D of step i+1 overlaps step i, D2H metric per step
+        """k serving steps through the public API. Every step's input goes host (pinned) -> device
+        and every step's result metric comes back device -> host inside the timed region. The copy
+        of step i+1's input runs on a second stream while step i computes, and the host reads step
+        i's result while step i+1 runs: the loop is never more than one step ahead of the results it
+        has read (a serving loop that overlaps post-processing with the next forward)."""
         cur = torch.cuda.current_stream()
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         done = [torch.cuda.Event(), torch.cuda.Event()]
+        got = [torch.cuda.Event(), torch.cuda.Event()]
+        results = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        sink = 0.0
         t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sync()
         t_begin.record(cur)
@@ -100,16 +106,22 @@ def _run(args, M, H, F) -> None:
             if i + 1 < k:
                 with torch.cuda.stream(copy_stream):
                     if i >= 1:
-                        copy_stream.wait_event(done[1 - bb])
+                        copy_stream.wait_event(done[1 - bb])      # step i-1 has finished with that buffer
                     x_bufs[1 - bb].copy_(x_host, non_blocking=True)
                     ready[1 - bb].record(copy_stream)
             cur.wait_event(ready[bb])
             y = step(x_bufs[bb])
             done[bb].record(cur)
-            result_host.copy_(y.float().abs().mean().reshape(1), non_blocking=True)
-            cur.synchronize()
+            results[bb].copy_(y.float().abs().mean().reshape(1), non_blocking=True)   # the step's metric, D2H
+            got[bb].record(cur)
+            if i >= 1:
+                got[1 - bb].synchronize()                         # step i-1's result is on the host
+                sink += float(results[1 - bb][0])
+        got[(k - 1) & 1].synchronize()
+        sink += float(results[(k - 1) & 1][0])
         t_end.record(cur)
         sync()
+        assert sink == sink                                        # the results were read (and are numbers)
         return t_begin.elapsed_time(t_end) / k
 
     def timed(fn, n):

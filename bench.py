@@ -81,7 +81,6 @@ def run_ours(args):
         xb.copy_(x_host)
         x_bufs.append(xb)
     x_symm = x_bufs[0]
-    result_host = torch.empty(1, dtype=torch.float32).pin_memory()
     copy_stream = torch.cuda.Stream()
 
     def sync():
@@ -95,11 +94,16 @@ def run_ours(args):
 
     def run_e2e(k):
         """k serving steps through the public API. Every step's input goes host (pinned) -> device
-        and every step's result metric comes back device -> host inside the timed region; the copy
-        of step i+1's input runs on a second stream while step i computes."""
+        and every step's result metric comes back device -> host inside the timed region. The copy
+        of step i+1's input runs on a second stream while step i computes, and the host reads step
+        i's result while step i+1 runs: the loop is never more than one step ahead of the results it
+        has read (a serving loop that overlaps post-processing with the next forward)."""
         cur = torch.cuda.current_stream()
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         done = [torch.cuda.Event(), torch.cuda.Event()]
+        got = [torch.cuda.Event(), torch.cuda.Event()]
+        results = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        sink = 0.0
         t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         sync()
         t_begin.record(cur)
@@ -118,10 +122,16 @@ def run_ours(args):
             cur.wait_event(ready[b])
             y = step(x_bufs[b])
             done[b].record(cur)
-            result_host.copy_(y.float().abs().mean().reshape(1), non_blocking=True)   # the step's metric, D2H
-            cur.synchronize()
+            results[b].copy_(y.float().abs().mean().reshape(1), non_blocking=True)   # the step's metric, D2H
+            got[b].record(cur)
+            if i >= 1:
+                got[1 - b].synchronize()                         # step i-1's result is on the host
+                sink += float(results[1 - b][0])
+        got[(k - 1) & 1].synchronize()
+        sink += float(results[(k - 1) & 1][0])
         t_end.record(cur)
         sync()
+        assert sink == sink                                        # the results were read (and are numbers)
         return t_begin.elapsed_time(t_end) / k
 
     def op_ag():

@@ -28,7 +28,12 @@ namespace kraken {
 constexpr int kRsReducerThreads = 192;   // six warps: with 12 warps per CTA the register budget per thread is the same as with 10
 constexpr int kRsPullThreads = kGemmThreads + kRsReducerThreads;
 
-__device__ __forceinline__ void reducer_bar_sync() { asm volatile("bar.sync 2, 192;" ::: "memory"); }
+// Named barriers of the two groups of 192 threads that reduce work items: 2 for the reducer warps,
+// 3 for the pipeline warps once they help.
+__device__ __forceinline__ void group_bar_sync(int group) {
+  if (group == 0) asm volatile("bar.sync 2, 192;" ::: "memory");
+  else asm volatile("bar.sync 3, 192;" ::: "memory");
+}
 
 // ---------------------------------------------------------------------------------------------
 // push: remote tiles go to the owner's staging slab, own tiles reduce in the epilogue
@@ -200,16 +205,16 @@ struct RsPullHooks : HookDefaults {
   // one 512-byte row segment per instruction. The item that finishes a tile last puts the tile's
   // counters back to zero. Not inlined: the reducer warps get their own register allocation
   // instead of sharing the epilogue's.
-  __device__ __noinline__ bool reduce_item(const GemmParams& p, int tr, int tc, int sub, int tid, int slot) {
+  __device__ __noinline__ bool reduce_item(const GemmParams& p, int tr, int tc, int sub, int tid, int slot, int group) {
     uint32_t* f = counter(p, p.rank, tr, tc);
     uint32_t* done = f + p.rs_done_off;
     const uint32_t need = (uint32_t)p.ws;
     if (tid == 0) {
-      trace_put(p, 2, slot, 0);
+      if (group == 0) trace_put(p, 2, slot, 0);
       spin_until([&] { return ld_acquire_sys(f) >= need; }, p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 57, 0, blockIdx.x));
-      trace_put(p, 2, slot, 1);
+      if (group == 0) trace_put(p, 2, slot, 1);
     }
-    reducer_bar_sync();
+    group_bar_sync(group);
     if (!status_ok(p.sync)) return false;
     const int N = p.rows_c;
     const int col0 = tc * bn;
@@ -250,24 +255,34 @@ struct RsPullHooks : HookDefaults {
     } else {
       reduce_loads<1, 8>(p, tid, total, vpr, lrow0, col0);
     }
-    reducer_bar_sync();                        // every thread's loads of this item have returned
+    group_bar_sync(group);                        // every thread's loads of this item have returned
     if (tid == 0) {
       if (atomicAdd(done, 1u) == (uint32_t)(kBM / p.rs_sub_rows - 1)) {
         *done = 0u;
         red_add_relaxed_sys(f, 0u - need);     // zero again for the call after next (the next uses the other bank)
       }
-      trace_put(p, 2, slot, 2);
+      if (group == 0) trace_put(p, 2, slot, 2);
     }
     return true;
   }
 
-  // Reducer warps. The work items of the own slab are numbered in the order their tiles are
-  // computed (tile_coords with pivot 0: row groups; inside a group column by column; inside a column
-  // the group's rows; virtual row v belongs to rank v % ws and is row tile rank*per_slab + v/ws; a
-  // pair tile: upper half first) and this CTA serves items me, me + num_ctas, ... . Item number ->
-  // tile costs one division: earlier versions that walked the tile order tile by tile (a serial
-  // integer chain on one warp) spent longer finding the next item than reducing it.
-  __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
+  // Work items. The items of the own slab are numbered in the order their tiles are computed
+  // (tile_coords with pivot 0: row groups; inside a group column by column; inside a column the
+  // group's rows; virtual row v belongs to rank v % ws and is row tile rank*per_slab + v/ws; a pair
+  // tile: upper half first) and this CTA serves items me, me + num_ctas, ... . Item number -> tile
+  // costs one division: earlier versions that walked the tile order tile by tile (a serial integer
+  // chain on one warp) spent longer finding the next item than reducing it. Two groups of 192
+  // threads take this CTA's items off one shared counter: the reducer warps from the start of the
+  // kernel, the six pipeline warps once their last tile is stored — so the items of the last wave,
+  // which nothing can overlap, are split between both groups.
+  __device__ __forceinline__ unsigned* claim_words() {
+    __shared__ unsigned words[4];      // [0] next item of this CTA; [1], [2] item just claimed by group 0 / 1
+    return words;
+  }
+  __device__ __forceinline__ void setup(const GemmParams&) { claim_words()[0] = 0u; }
+
+  __device__ __forceinline__ void serve_items(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid,
+                                              int group) {
     const unsigned halves = half < 0 ? 1u : 2u;
     const unsigned me = half < 0 ? worker : 2u * worker + (unsigned)half;
     const unsigned num_ctas = num_workers * halves;
@@ -277,15 +292,22 @@ struct RsPullHooks : HookDefaults {
     const unsigned sub_shift = (unsigned)__ffs((int)subs) - 1u;
     const int per_slab = p.tiles_r / p.ws;                            // row tiles (of this kernel's tile height) per slab
     const unsigned total_items = ((unsigned)per_slab * (unsigned)p.tiles_c) << tile_shift;
-    // current row group: [first, gend), its own rows v0, v0 + ws, ... (n_g of them), ordinal of its first own tile
-    int first = 0, gend = min(p.group_r, p.tiles_r);
-    int v0 = (p.rank % p.ws);
-    int n_g = v0 < gend ? (gend - 1 - v0) / p.ws + 1 : 0;
-    unsigned o_base = 0;
+    const unsigned my_items = me < total_items ? (total_items - me + num_ctas - 1u) / num_ctas : 0u;
+    unsigned* words = claim_words();
     int served = 0;
-    for (unsigned id = me; id < total_items; id += num_ctas) {
+    while (true) {
+      if (tid == 0) words[1 + group] = atomicAdd(&words[0], 1u);
+      group_bar_sync(group);
+      const unsigned i = words[1 + group];
+      if (i >= my_items) break;
+      const unsigned id = me + i * num_ctas;
       const unsigned o = id >> tile_shift, k = id & (per_tile - 1u);
-      while (o >= o_base + (unsigned)(n_g * p.tiles_c)) {             // advance to the group that holds tile o
+      // the row group that holds own tile o: [first, gend), its own rows v0, v0 + ws, ... (n_g of them)
+      int first = 0, gend = min(p.group_r, p.tiles_r);
+      int v0 = p.rank % p.ws;
+      int n_g = v0 < gend ? (gend - 1 - v0) / p.ws + 1 : 0;
+      unsigned o_base = 0;
+      while (o >= o_base + (unsigned)(n_g * p.tiles_c)) {
         o_base += (unsigned)(n_g * p.tiles_c);
         first += p.group_r;
         gend = min(first + p.group_r, p.tiles_r);
@@ -296,8 +318,14 @@ struct RsPullHooks : HookDefaults {
       const int tc = idx / n_g, j = idx - tc * n_g;
       const int trv = p.rank * per_slab + v0 / p.ws + j;              // (v0 + j*ws) / ws
       const int tr = half < 0 ? trv : 2 * trv + (int)(k >> sub_shift);
-      if (tr * kBM < p.rows_r && !reduce_item(p, tr, tc, (int)(k & (subs - 1u)), tid, served++)) return;
+      if (tr * kBM < p.rows_r && !reduce_item(p, tr, tc, (int)(k & (subs - 1u)), tid, served++, group)) return;
     }
+  }
+  __device__ __forceinline__ void side_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
+    serve_items(p, worker, num_workers, half, tid, 0);
+  }
+  __device__ __forceinline__ void helper_role(const GemmParams& p, unsigned worker, unsigned num_workers, int half, int tid) {
+    if (blockDim.x > (unsigned)kGemmThreads) serve_items(p, worker, num_workers, half, tid, 1);
   }
 };
 

@@ -169,12 +169,17 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 //   row-major path only), after_store (what happens once the tile is stored), may_wait (whether
 //   begin_tile of that row tile can block on another rank: the main loop then first runs any
 //   completion hook it still holds back, so that no rank waits while it withholds a signal),
-//   side_role (work of the warps beyond the six pipeline warps, if the launch has any).
+//   side_role (work of the warps beyond the six pipeline warps, if the launch has any),
+//   helper_role (what the six pipeline warps do after their last tile, before the teardown).
 struct HookDefaults {
   __device__ __forceinline__ bool may_wait(const GemmParams&, int) const { return false; }
   // worker / num_workers: this CTA (or CTA pair) among those of the launch; half: -1 for a single
   // CTA, else the CTA's rank inside its pair; tid: thread index among the side-role warps.
   __device__ __forceinline__ void side_role(const GemmParams&, unsigned, unsigned, int, int) {}
+  // setup: thread 0, before the block's first barrier. helper_role: the six pipeline warps once
+  // their own roles are over (all tiles of this CTA computed and stored), tid in [0, 192).
+  __device__ __forceinline__ void setup(const GemmParams&) {}
+  __device__ __forceinline__ void helper_role(const GemmParams&, unsigned, unsigned, int, int) {}
 };
 
 struct TileDest {
@@ -393,6 +398,7 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       mbar_init(tempty_bar(a), 4);
     }
     mbar_fence_init();
+    hooks.setup(p);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -521,6 +527,8 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
     }
   }
 
+  if (warp < 6) hooks.helper_role(p, bid, nb, -1, (int)threadIdx.x);
+
   // ---- teardown: every role arrives here, on the normal path and after a failed wait
   tc_fence_before();
   __syncthreads();
@@ -584,6 +592,7 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       mbar_init(tempty_bar(a), 8);
     }
     mbar_fence_init();
+    hooks.setup(p);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -722,6 +731,8 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
       if (ok) hooks.after_store(p, prev_tr, prev_tc, q, lane);
     }
   }
+
+  if (warp < 6) hooks.helper_role(p, pair_id, num_pairs, (int)cta, (int)threadIdx.x);
 
   // ---- teardown: nobody leaves while the pair may still touch its shared memory or barriers
   tc_fence_before();

@@ -11,10 +11,12 @@ kraken/comm/two_shot_all_reduce.py:153).
 ``KRAKEN_GEMM_PAIR``        ``0`` forces the single-CTA GEMM kernel (default: CTA pairs when eligible)
 ``KRAKEN_GEMM_GROUP``       row tiles per column sweep of the GEMM tile order (default 16)
 ``KRAKEN_TMA_STORE``        ``0`` makes the GEMM epilogue use vector stores instead of TMA stores
-``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``auto`` (default: ``push`` at 2 ranks, ``ce`` above),
+``KRAKEN_AG_MODE``          engine of the fused all-gather GEMM: ``auto`` (default: ``push``; ``ce`` above 2 ranks when
+                            the workspace has no multicast mapping),
                             ``push`` (comm CTAs write the own shard into the peers' gathered buffers), ``ce`` (copy
                             engines + stream flags) or ``sm`` (comm CTAs pull the peers' shards)
-``KRAKEN_AG_MC``            ``1``: the push engine writes once through the NVSwitch (multimem.st) when a multicast mapping exists
+``KRAKEN_AG_MC``            ``0`` / ``1``: whether the push engine writes once through the NVSwitch (multimem.st); default:
+                            above 2 ranks when a multicast mapping exists
 ``KRAKEN_RS_ALGO``          ``scatter`` (default: tiles are stored into the owner's staging, reducer warps sum local
                             memory), ``pull`` (reducer warps sum the ranks' staged tiles with peer loads) or
                             ``push`` (tiles are stored into the owner's staging and summed in its epilogue)
@@ -71,11 +73,16 @@ def ag_mode() -> str:
     return v if v in ("auto", "push", "sm", "ce") else "auto"
 
 
-def ag_multicast() -> bool:
+def ag_multicast(world_size: int) -> bool:
     """Whether the push engine of the all-gather GEMM writes through the NVSwitch (multimem.st) when
-    the gathered buffer has a multicast mapping (KRAKEN_AG_MC, default 0: measured at 2 GPUs a comm CTA
-    forwards about 10 GB/s with multimem.st, half of what it reaches with bulk stores to one peer)."""
-    return os.environ.get("KRAKEN_AG_MC", "0") == "1"
+    the gathered buffer has a multicast mapping. Default: above 2 ranks. A comm CTA forwards about
+    10 GB/s with multimem.st and about 20 GB/s with bulk stores to one peer, but the multicast form
+    sends one copy instead of ws - 1: measured fastest engine at 8 GPUs (359 us against 371 us for
+    the copy engines at M = 8192), slower than peer-by-peer stores at 2. KRAKEN_AG_MC=0/1 forces."""
+    v = os.environ.get("KRAKEN_AG_MC", "")
+    if v in ("0", "1"):
+        return v == "1"
+    return world_size > 2
 
 
 def rs_algo() -> str:

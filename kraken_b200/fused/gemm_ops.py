@@ -83,17 +83,15 @@ def _default_comm_ctas(n_local: int, ws: int) -> int:
 def _default_push_ctas(shard_bytes: int, ws: int, flops: float, multicast: bool) -> int:
     """Comm CTAs of the PUSH engine. Unicast: each rank writes ws copies of its shard during the GEMM
     and a comm CTA (local memory -> shared memory -> peer, bounded by what its shared memory keeps
-    in flight) was measured at about 20 GB/s. Multicast: one copy, forwarded from registers, taken
-    as 40 GB/s per comm CTA; it should be done in about half the GEMM's time, since every peer's
-    shard arrives at the same pace. KRAKEN_NUM_COMM_SMS overrides."""
+    in flight) was measured at about 20 GB/s. Multicast: one copy, forwarded from registers at about
+    10 GB/s per comm CTA. KRAKEN_NUM_COMM_SMS overrides."""
     import os
 
     if "KRAKEN_NUM_COMM_SMS" in os.environ:
         return config.num_comm_sms()
     t_gemm = flops / 1.45e15
     if multicast:
-        rate = shard_bytes / max(0.5 * t_gemm, 1e-6)
-        n = int(-(-rate // 40e9))
+        return 8           # measured at 8 GPUs: 4 starve the GEMM, 16 cost more SMs than they save (M = 2048 and 8192)
     else:
         rate = ws * shard_bytes / max(t_gemm, 1e-6)
         n = int(-(-rate // 20e9))
@@ -150,10 +148,11 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     dev = a_shared.device
     backend = kwargs.get("backend", config.ag_mode())
     if backend == "auto":
-        # Measured: a comm CTA moves 10-20 GB/s (what its shared memory keeps in flight), so pushing
-        # ws copies of a shard needs 8 CTAs at 2 ranks and far too many at 8; the copy engines move the
-        # same bytes at link rate without using an SM.
-        backend = "push" if ws <= 2 else "ce"
+        # Measured: a comm CTA moves 10-20 GB/s (what its shared memory keeps in flight). Pushing
+        # ws - 1 copies of a shard peer by peer needs 8 CTAs at 2 ranks and far too many at 8; ONE
+        # multicast copy through the NVSwitch needs 8 at any world size and was the fastest engine at
+        # 8 GPUs. Without a multicast mapping the copy engines take over above 2 ranks.
+        backend = "push" if (ws <= 2 or (config.nvls_enabled() and config.ag_multicast(ws))) else "ce"
     if backend not in ("push", "ce", "sm"):
         raise ValueError("backend must be 'push', 'ce' or 'sm'")
     emu = hdl.group.emu
@@ -189,9 +188,10 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
             off = (calls & 1) * half
             gathered = oh.get_buffer(rank, (M, K), torch.bfloat16, storage_offset=off // 2)
         flag_base = config.TILE_FLAG_BASE + (calls & 1) * _AG_FLAG_BANK
-        use_mc = bool(oh.multicast_ptr) and bool(kwargs.get("multicast", config.ag_multicast()))
-        if use_mc and progress is None and "splits_per_rank" not in kwargs and shard_rows % 1024 == 0:
-            splits = 4                      # all shards arrive at the same pace: finer chunks let the GEMM start sooner
+        use_mc = bool(oh.multicast_ptr) and bool(kwargs.get("multicast", config.ag_multicast(ws)))
+        if use_mc and progress is None and "splits_per_rank" not in kwargs:
+            # all shards arrive at the same pace: finer chunks let the GEMM start sooner
+            splits = 4 if shard_rows % 1024 == 0 else (2 if shard_rows % 256 == 0 else 1)
         mc_out = oh.multicast_ptr + off if use_mc else None
         mc_flags = oh.multicast_ptr + oh.buffer_size + 4 * flag_base if use_mc else None
         n_comm = int(kwargs.get("num_comm_sms", 0)) or _default_push_ctas(shard_rows * K * 2, ws, 2.0 * M * N * K, use_mc)
