@@ -114,7 +114,9 @@ def _two_shot(tensor: torch.Tensor, bias, out: torch.Tensor | None, kwargs, use_
     if out is None:
         out = torch.empty_like(tensor)
     bias_ptr, bias_n = _bias_args(bias, tensor)
-    mc = hdl.multicast_ptr if (use_mc and hdl.multicast_ptr) else None
+    # in-switch reduction pays from 4 ranks on: at 2 ranks the peer-load form was measured faster
+    # (731 us against 1007 us at 256 MB), at 8 it is 1.8x slower than the NVLS form
+    mc = hdl.multicast_ptr if (use_mc and hdl.multicast_ptr and hdl.world_size > 2) else None
     _dump(f"two_shot_all_reduce numel={tensor.numel()} ws={hdl.world_size} nvls={bool(mc)}", hdl)
     _lib.check(_lib.lib().kr_two_shot_all_reduce(
         hdl.buffer_ptrs_dev, 0, hdl.signal_pad_ptrs_dev, hdl.rank, hdl.world_size, tensor.data_ptr(), out.data_ptr(),
@@ -126,7 +128,8 @@ def two_shot_all_reduce(tensor: torch.Tensor, **kwargs) -> torch.Tensor:
     """output = sum over ranks of `tensor` (an ordinary tensor: it is staged through the group's
     symmetric workspace). Each rank reduces 1/ws of the data and publishes it to all ranks — with
     ``multimem.ld_reduce`` / ``multimem.st`` through the NVSwitch when the workspace has a multicast
-    mapping (measured 1.8x the peer-load form at 256 MB on 8 GPUs), else with peer loads and stores.
+    mapping and there are more than 2 ranks (measured 1.8x the peer-load form at 256 MB on 8 GPUs,
+    but slower than it on 2), else with peer loads and stores.
     kwargs: group, max_num_blocks, nvls=False forces the peer-load form (as does
     KRAKEN_FORCE_ALGO=two_shot)."""
     if tensor.device.type != "cuda":
