@@ -147,15 +147,16 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
         splits = 1
     dev = a_shared.device
     backend = kwargs.get("backend", config.ag_mode())
+    emu = hdl.group.emu
     if backend == "auto":
         # Measured: a comm CTA moves 10-20 GB/s (what its shared memory keeps in flight). Pushing
         # ws - 1 copies of a shard peer by peer needs 8 CTAs at 2 ranks and far too many at 8; ONE
         # multicast copy through the NVSwitch needs 8 at any world size and was the fastest engine at
         # 8 GPUs. Without a multicast mapping the copy engines take over above 2 ranks.
-        backend = "push" if (ws <= 2 or (config.nvls_enabled() and config.ag_multicast(ws))) else "ce"
+        mc_ok = config.nvls_enabled() and config.ag_multicast(ws) and emu is None and bool(_lib.lib().kr_symm_multicast_supported())
+        backend = "push" if (ws <= 2 or mc_ok) else "ce"
     if backend not in ("push", "ce", "sm"):
         raise ValueError("backend must be 'push', 'ce' or 'sm'")
-    emu = hdl.group.emu
     if backend == "ce" and (emu is not None or ws == 1):
         backend = "sm"
     if backend == "push" and (ws == 1 or ws * splits > _AG_FLAG_BANK):
