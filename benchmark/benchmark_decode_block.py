@@ -19,6 +19,8 @@ def main():
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--save-path", default="results/bench_decode_block")
+    ap.add_argument("--variants", action="store_true",
+                    help="also time every exchange (push / one_shot / two_shot) with 1 and 2 K splits")
     args = ap.parse_args()
     rank, ws, dev = setup()
     from kraken_b200 import fused
@@ -60,6 +62,14 @@ def main():
             "ar_bias_norm_one_shot": lambda: fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5),
             "nccl_add_norm": nccl_norm,
         }
+        if args.variants:
+            for algo in ("push", "one_shot", "two_shot"):
+                for ks in (1, 2):
+                    if algo == "one_shot" and ks == 2:
+                        continue
+                    backends[f"gemm_ar_{algo}_k{ks}"] = (
+                        lambda algo=algo, ks=ks: fused.gemm_one_shot_all_reduce_fused(a, b, algo=algo, k_splits=ks))
+
         def chain():
             # the decode step this benchmark is about: GEMM + all-reduce, then the next layer's
             # all-reduce + bias + RMSNorm, back to back on one stream

@@ -98,6 +98,14 @@ struct alignas(64) GemmParams {
   unsigned long long res_off;     // two-shot: reduced result [M][N] fp32
   uint32_t flag2_base;            // two-shot: "result published" flags
   void* mc_ptr;                   // multicast address of the staging buffer (NVLS) or nullptr
+  // Split-K (single-CTA kernels): with k_splits > 1 the persistent index runs over
+  // k_splits * tiles work items, item = split * tiles + tile, and an item multiplies only the K
+  // blocks of its split; the hooks see the split as Hooks::k_split and combine the partial sums.
+  int k_splits;
+  // AR, tagged push: this call's tag (never 0) and the byte offset of its slot array
+  // [ws * k_splits][M][N] of {fp32 value, tag} pairs inside every rank's staging buffer
+  uint32_t ll_tag;
+  unsigned long long ll_off;
   // RS
   int slab_rows;             // M / ws
   int rs_algo;               // 0: push, owner reduces in its epilogue; 1: pull; 2: scatter (push + reducer warps)
@@ -172,6 +180,7 @@ __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;"
 //   side_role (work of the warps beyond the six pipeline warps, if the launch has any),
 //   helper_role (what the six pipeline warps do after their last tile, before the teardown).
 struct HookDefaults {
+  int k_split = 0;           // which K split the tile in hand belongs to (set by the main loop)
   __device__ __forceinline__ bool may_wait(const GemmParams&, int) const { return false; }
   // worker / num_workers: this CTA (or CTA pair) among those of the launch; half: -1 for a single
   // CTA, else the CTA's rank inside its pair; tid: thread index among the side-role warps.
@@ -189,6 +198,11 @@ struct TileDest {
   int rows, cols;    // destination bounds
   const CUtensorMap* tmap;   // bf16 destination as a tensor map (box 64 columns x 32 rows, 128-byte
                              // swizzle) for TMA stores, or nullptr: plain vector stores
+  // Tagged push (transposed fp32 tiles only): when ll_tag != 0 every element goes, as an 8-byte
+  // {value, tag} pair, to byte offset ll_off + 8 * (row * ld + column) of EVERY rank's staging
+  // buffer (GemmParams::peer_buf) instead of to `base`.
+  uint32_t ll_tag = 0;
+  unsigned long long ll_off = 0;
 };
 
 // Epilogue of one tile, run by the four epilogue warps: TMEM -> registers -> (hook: add peers'
@@ -223,7 +237,11 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
         for (int j = 0; j < CH; ++j) {
           const int drow = dst.col0 + c0 + j;
           if (drow < dst.rows) {
-            if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
+            if (dst.ll_tag != 0) {
+              const unsigned long long o = dst.ll_off + 8ull * ((unsigned long long)drow * dst.ld + dcol);
+              const unsigned long long v = ((unsigned long long)dst.ll_tag << 32) | r[j];
+              for (int d = 0; d < p.ws; ++d) st_relaxed_sys_u64((char*)p.peer_buf[d] + o, v);
+            } else if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
             else ((__nv_bfloat16*)dst.base)[(long long)drow * dst.ld + dcol] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
@@ -409,8 +427,17 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.tiles_r * p.tiles_c;
+  const int tiles_rc = p.tiles_r * p.tiles_c;
+  const int ksp = p.k_splits > 1 ? p.k_splits : 1;
+  const int total_tiles = tiles_rc * ksp;
   const int num_kb = (p.K + kStageK - 1) / kStageK;
+  // work item t -> (tile, K-block range): split-major, so one wave of CTAs covers every tile once
+  auto item_of = [&](int t, int& tile, int& split, int& kb_lo, int& kb_hi) {
+    split = ksp > 1 ? t / tiles_rc : 0;
+    tile = t - split * tiles_rc;
+    kb_lo = (int)((long long)num_kb * split / ksp);
+    kb_hi = (int)((long long)num_kb * (split + 1) / ksp);
+  };
 
   if (warp == 0) {
     // ================= TMA producer =================
@@ -421,12 +448,13 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
       uint32_t ph = 0;
       bool ok = true;
       for (int t = bid; t < total_tiles && ok; t += nb) {
-        int tr, tc;
-        tile_coords(p, t, tr, tc);
+        int tr, tc, tile, split, kb_lo, kb_hi;
+        item_of(t, tile, split, kb_lo, kb_hi);
+        tile_coords(p, tile, tr, tc);
         const CUtensorMap* rmap = &p.tmap_r;
         int row0 = tr * kBM;
         ok = hooks.before_load(p, tr, rmap, row0);
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi && ok; ++kb) {
           ok = mbar_wait(empty_bar(s), ph ^ 1u, p.sync, 40);
           if (!ok) break;
           mbar_expect_tx(full_bar(s), Cfg::A_BYTES + Cfg::B_BYTES);
@@ -453,18 +481,20 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
         tc_fence_after();
         trace_put(p, 0, it, 0);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int tile, split, kb_lo, kb_hi;
+        item_of(t, tile, split, kb_lo, kb_hi);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           ok = mbar_wait(full_bar(s), ph, p.sync, 42);
           if (!ok) break;
           tc_fence_after();
-          if (kb == 0) trace_put(p, 0, it, 1);
+          if (kb == kb_lo) trace_put(p, 0, it, 1);
           const uint32_t sa = stage0 + s * Cfg::STAGE;
           const uint64_t adesc = make_smem_desc_sw128(sa);
           const uint64_t bdesc = make_smem_desc_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            if (ELT == 2) umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            if (ELT == 2) umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb_lo || k != 0) ? 1u : 0u);
+            else umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > kb_lo || k != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(s));   // frees the stage once these MMAs have read it
           if (++s == Cfg::STAGES) { s = 0; ph ^= 1u; }
@@ -485,8 +515,10 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
     int it = 0;
     bool ok = true;
     for (int t = bid; t < total_tiles && ok; t += nb, ++it) {
-      int tr, tc;
-      tile_coords(p, t, tr, tc);
+      int tr, tc, tile, split, kb_lo, kb_hi;
+      item_of(t, tile, split, kb_lo, kb_hi);
+      tile_coords(p, tile, tr, tc);
+      hooks.k_split = split;
       const int acc = it & 1;
       const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
       ok = mbar_wait(tfull_bar(acc), acc_ph, p.sync, 43);
@@ -527,6 +559,9 @@ __device__ __forceinline__ void gemm_mainloop(const GemmParams& p, unsigned bid,
     }
   }
 
+  // The producer and MMA warps ran their roles on one elected lane: wait for it, so that the other
+  // lanes do not start polling in the helper role while it still has tiles to feed.
+  __syncwarp();
   if (warp < 6) hooks.helper_role(p, bid, nb, -1, (int)threadIdx.x);
 
   // ---- teardown: every role arrives here, on the normal path and after a failed wait
@@ -732,6 +767,9 @@ __device__ __forceinline__ void gemm_mainloop_pair(const GemmParams& p, unsigned
     }
   }
 
+  // The producer and MMA warps ran their roles on one elected lane: wait for it, so that the other
+  // lanes do not start polling in the helper role while it still has tiles to feed.
+  __syncwarp();
   if (warp < 6) hooks.helper_role(p, pair_id, num_pairs, (int)cta, (int)threadIdx.x);
 
   // ---- teardown: nobody leaves while the pair may still touch its shared memory or barriers

@@ -36,15 +36,122 @@ struct ArHooks : HookDefaults {
   __device__ __forceinline__ int tile_of(const GemmParams& p, int tr, int tc) const { return tr * p.tiles_c + tc; }
   __device__ __forceinline__ TileDest tile_dest(const GemmParams& p, int tr, int tc) {
     char* base;
+    const int slot = p.rank * nsplit(p) + k_split;
+    const size_t mn = (size_t)p.out_rows * p.out_cols;
+    if (p.ar_algo == 2) {
+      TileDest d{nullptr, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
+      d.ll_tag = p.ll_tag;
+      d.ll_off = p.ll_off + (unsigned long long)slot * mn * 8ull;
+      return d;
+    }
     if (p.ar_algo == 0) {
       base = (char*)p.bufs[p.rank] + p.stage_off;
     } else {
       const int owner = tile_of(p, tr, tc) % p.ws;
-      base = (char*)p.bufs[owner] + p.part_off + (size_t)p.rank * p.out_rows * p.out_cols * 4;
+      base = (char*)p.bufs[owner] + p.part_off + (size_t)slot * mn * 4;
     }
     return TileDest{base, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
   }
-  // region of tile (tr, tc) in the orientation of `out`
+  __device__ __forceinline__ int nsplit(const GemmParams& p) const { return p.k_splits > 1 ? p.k_splits : 1; }
+  // Tagged push: the epilogue has already written this CTA's partial tiles, as {value, tag} pairs,
+  // into slot [rank * splits + split] of every rank's staging. Once all of this CTA's tiles are out
+  // (so that no CTA ever waits while it still owes a peer data), the six pipeline warps sum, for
+  // each work item of the CTA, that item's share of its tile over all ws * splits slots of the OWN
+  // staging, polling each pair until it carries this call's tag. No flag, no fence: the 8-byte pair
+  // is one atomic store. Slots are summed in slot order, so every rank gets identical bits.
+  __device__ __forceinline__ void helper_role(const GemmParams& p, unsigned bid, unsigned nb, int, int tid) {
+    if (p.ar_algo != 2) return;
+    const int ks = nsplit(p), nslots = p.ws * ks;
+    const int tiles_rc = p.tiles_r * p.tiles_c;
+    const size_t mn = (size_t)p.out_rows * p.out_cols;
+    const char* mine = (const char*)p.peer_buf[p.rank] + p.ll_off;
+    for (int t = (int)bid; t < tiles_rc * ks; t += (int)nb) {
+      const int split = t / tiles_rc;
+      int tr, tc;
+      tile_coords(p, t - split * tiles_rc, tr, tc);
+      int r_lo, r_n, c_lo, c_n;
+      region(p, tr, tc, r_lo, r_n, c_lo, c_n);
+      if (r_lo + r_n > p.out_rows) r_n = p.out_rows - r_lo;
+      if (r_n <= 0) continue;
+      const int n = r_n * c_n;
+      const char* tile_src = mine;
+      if ((p.out_cols & 1) == 0) {
+        // Four consecutive elements per thread and step: their {value, tag} pairs are two 16-byte
+        // loads per slot, so one poll keeps up to eight loads in flight instead of one element's.
+        const int nq = n / 4;                 // c_n = 128: rows are whole quads
+        const int lo = (int)((long long)nq * split / ks), hi = (int)((long long)nq * (split + 1) / ks);
+        for (int qd = lo + tid; qd < hi; qd += kGemmThreads) {
+          const int i = qd * 4;
+          const int rr = r_lo + i / c_n, cc = c_lo + i % c_n;
+          if (cc >= p.out_cols) continue;
+          const int nv = p.out_cols - cc < 4 ? p.out_cols - cc : 4;     // 2 or 4 (out_cols is even)
+          const char* src = tile_src + ((size_t)rr * p.out_cols + cc) * 8;
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int s0 = 0; s0 < nslots; s0 += 4) {
+            unsigned long long v[4][4];
+            const bool ok = spin_until(
+                [&] {
+                  bool all = true;
+#pragma unroll
+                  for (int k = 0; k < 4; ++k)
+                    if (s0 + k < nslots) {
+                      const char* q = src + (size_t)(s0 + k) * mn * 8;
+                      ld_relaxed_sys_u64x2(q, v[k][0], v[k][1]);
+                      if (nv == 4) ld_relaxed_sys_u64x2(q + 16, v[k][2], v[k][3]);
+#pragma unroll
+                      for (int e = 0; e < 4; ++e)
+                        if (e < nv) all = all && (uint32_t)(v[k][e] >> 32) == p.ll_tag;
+                    }
+                  return all;
+                },
+                p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 52, 0, blockIdx.x));
+            if (!ok) return;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (s0 + k < nslots) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (e < nv) acc[e] += __uint_as_float((uint32_t)v[k][e]);
+              }
+          }
+          float* o = (float*)p.out + (size_t)rr * p.ldo + cc;
+          if (nv == 4 && (((uintptr_t)o) & 15) == 0) {
+            *(float4*)o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          } else {
+            for (int e = 0; e < nv; ++e) o[e] = acc[e];
+          }
+        }
+        continue;
+      }
+      const int lo = (int)((long long)n * split / ks), hi = (int)((long long)n * (split + 1) / ks);
+      for (int i = lo + tid; i < hi; i += kGemmThreads) {
+        const int rr = r_lo + i / c_n, cc = c_lo + i % c_n;
+        if (cc >= p.out_cols) continue;
+        const char* src = mine + ((size_t)rr * p.out_cols + cc) * 8;
+        float acc = 0.f;
+        for (int s0 = 0; s0 < nslots; s0 += 8) {
+          unsigned long long v[8];
+          const bool ok = spin_until(
+              [&] {
+                bool all = true;
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  if (s0 + k < nslots) {
+                    v[k] = ld_relaxed_sys_u64(src + (size_t)(s0 + k) * mn * 8);
+                    all = all && (uint32_t)(v[k] >> 32) == p.ll_tag;
+                  }
+                return all;
+              },
+              p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 52, 0, blockIdx.x));
+          if (!ok) return;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (s0 + k < nslots) acc += __uint_as_float((uint32_t)v[k]);
+        }
+        ((float*)p.out)[(size_t)rr * p.ldo + cc] = acc;
+      }
+    }
+  }
   __device__ __forceinline__ void region(const GemmParams& p, int tr, int tc, int& r_lo, int& r_n, int& c_lo, int& c_n) {
     if (p.transposed) { r_lo = tc * bn; r_n = bn; c_lo = tr * kBM; c_n = kBM; }
     else { r_lo = tr * kBM; r_n = kBM; c_lo = tc * bn; c_n = bn; }
@@ -58,8 +165,10 @@ struct ArHooks : HookDefaults {
     return false;
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
+    if (p.ar_algo == 2) return true;   // tagged push: nothing to signal, the sums happen in helper_role
     const int tile = tile_of(p, tr, tc);
     const int tid = q * 32 + lane;   // 0..127 over the epilogue warps
+    const int ks = nsplit(p), nslots = p.ws * ks;
     int r_lo, r_n, c_lo, c_n;
     region(p, tr, tc, r_lo, r_n, c_lo, c_n);
     const int upr = c_n / 4;         // 16-byte units per tile row
@@ -131,8 +240,9 @@ struct ArHooks : HookDefaults {
     // ---------------- two-shot ----------------
     const int owner = tile % p.ws;
     if (tid == 0) red_add_release_sys(p.pads[owner] + p.flag_base + tile, 1u);
+    if (k_split != 0) return true;   // split-K: the CTA of split 0 reduces (owner) or copies out (others)
     if (owner == p.rank) {
-      if (tid == 0) wait_count(p.pads[p.rank] + p.flag_base + tile, (uint32_t)p.ws, p, 58);
+      if (tid == 0) wait_count(p.pads[p.rank] + p.flag_base + tile, (uint32_t)nslots, p, 58);
       epi_bar_sync();
       if (!status_ok(p.sync)) return false;
       const char* part = (const char*)p.bufs[p.rank] + p.part_off;
@@ -143,13 +253,13 @@ struct ArHooks : HookDefaults {
         if (vec) {
           U4 x[8];
           float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s0 = 0; s0 < p.ws; s0 += 8) {
+          for (int s0 = 0; s0 < nslots; s0 += 8) {
 #pragma unroll
             for (int s = 0; s < 8; ++s)
-              if (s0 + s < p.ws) x[s] = ld16(part + (size_t)(s0 + s) * mn4 + off);
+              if (s0 + s < nslots) x[s] = ld16(part + (size_t)(s0 + s) * mn4 + off);
 #pragma unroll
             for (int s = 0; s < 8; ++s)
-              if (s0 + s < p.ws) {
+              if (s0 + s < nslots) {
                 a.x += __uint_as_float(x[s].x); a.y += __uint_as_float(x[s].y);
                 a.z += __uint_as_float(x[s].z); a.w += __uint_as_float(x[s].w);
               }
@@ -168,7 +278,7 @@ struct ArHooks : HookDefaults {
         } else {
           for (int e = 0; e < 4 && cc + e < p.out_cols; ++e) {
             float acc = 0.f;
-            for (int s = 0; s < p.ws; ++s) acc += ((const float*)(part + (size_t)s * mn4 + off))[e];
+            for (int s = 0; s < nslots; ++s) acc += ((const float*)(part + (size_t)s * mn4 + off))[e];
             ((float*)p.out)[(size_t)rr * p.ldo + cc + e] = acc;
             for (int s = 1; s < p.ws; ++s)
               ((float*)((char*)p.bufs[(p.rank + s) % p.ws] + p.res_off + off))[e] = acc;

@@ -117,7 +117,7 @@ KR_API int kr_symm_multicast_supported() {
   return multicast_supported(dev);
 }
 
-// Creates this rank's block: `bytes` of data followed by `pad_bytes` of zeroed signal pad. The
+// Creates this rank's block: `bytes` of data followed by `pad_bytes` of signal pad, all zeroed. The
 // block is usable locally at once; kr_symm_set_group + import + finalize make it symmetric.
 KR_API int kr_symm_alloc(unsigned long long bytes, unsigned long long pad_bytes, void** out) {
   KR_REQUIRE(pad_bytes % 16 == 0, "signal pad size must be a multiple of 16");
@@ -149,7 +149,10 @@ KR_API int kr_symm_alloc(unsigned long long bytes, unsigned long long pad_bytes,
   int rc = map_rw(&va, a->local_handle, a->total, gran, a->device);
   if (rc) return rc;
   a->local_ptr = va;
-  KR_CUDA(cudaMemset((void*)(va + a->data_bytes), 0, a->pad_bytes));
+  // The whole block starts out zero: the signal pad has to, and ops that tag their data (the decode
+  // GEMM -> all-reduce's tagged push) rely on never meeting a stale tag in fresh memory. No peer can
+  // have written yet: the block is not shared before the exchange that follows.
+  KR_CUDA(cudaMemset((void*)va, 0, a->total));
   KR_CUDA(cudaDeviceSynchronize());
   *out = a;
   return KR_SUCCESS;

@@ -230,16 +230,25 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     return a_out, c
 
 
+_AR_ALGOS = {"one_shot": 0, "two_shot": 1, "push": 2}
+
+
 def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
     """fp32 [M, N] = all_reduce(a @ b): each rank holds a K-shard of both operands. One kernel:
-    the GEMM epilogue exchanges fp32 partial tiles behind per-tile flags (no grid-wide barrier).
-    Small outputs use the one-shot form (every rank sums the tile from all ranks, in the NVSwitch
-    when the staging buffer has a multicast mapping); larger ones the two-shot form (tile owner
-    t % ws receives all partials, sums them in rank order and publishes the result), which moves
-    ws/2 times fewer bytes. Every rank gets identical bits. Decode-sized M puts the weights on the
-    128-row side of the MMA. bf16 operands use the bf16 tensor-core path; fp32 x fp32 operands are
-    multiplied as tf32 (what ``tl.dot`` does for the reference's fp32 tests); anything else is cast
-    to bf16. kwargs: group, swap_ab, algo="one_shot"|"two_shot"."""
+    the GEMM epilogue exchanges fp32 partial tiles; there is no grid-wide barrier. Three exchanges:
+    "push" (decode-sized M) — the epilogue writes every partial element, paired with a per-call tag
+    in one 8-byte store, straight into a slot of every rank's staging; each rank then sums its own
+    slots as the tagged pairs land (no flag, no fence, one NVLink crossing); "one_shot" — the
+    partial tile goes to the own staging, a flag to every peer, and every rank sums the tile from
+    all ranks (in the NVSwitch when the staging buffer has a multicast mapping); "two_shot" (larger
+    outputs) — tile owner t % ws receives all partials, sums them in rank order and publishes the
+    result, which moves ws/2 times fewer bytes. Small M also splits K over several CTAs per tile so
+    that more SMs stream the weights; the splits are extra slots of the same exchange. The launcher
+    picks exchange and split count by a cost model. Every rank gets identical bits. Decode-sized M
+    puts the weights on the 128-row side of the MMA. bf16 operands use the bf16 tensor-core path;
+    fp32 x fp32 operands are multiplied as tf32 (what ``tl.dot`` does for the reference's fp32
+    tests); anything else is cast to bf16.
+    kwargs: group, swap_ab, algo="push"|"one_shot"|"two_shot", k_splits=1..4."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_all_reduce(a, b, group)
@@ -257,19 +266,35 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
         _lib.check(L.kr_gemm_bf16(a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K, 1, -1, 0, 0, 1,
                                   1 if tf32 else 0, _lib.current_stream_ptr()))
         return out
-    need = 2 * (info.world_size + 1) * M * N * 4
+    ws = info.world_size
+    mn4 = M * N * 4
+    # one-shot: an eighth of the buffer per staging half; two-shot: ws partial slots + the result in
+    # the upper half (twice the slots for decode-sized outputs, so that K can be split in two)
+    need = max(8 * mn4, 2 * (ws + 1) * mn4, 2 * (2 * ws + 1) * mn4 if mn4 <= (4 << 20) else 0)
+    # tagged push: ws * k_splits slots of {value, tag} pairs in an eighth of the buffer; sized for when
+    # it is asked for, and up to 64 MB so that the cost model may pick it for decode-sized outputs
+    ll = 8 * ws * max(int(kwargs.get("k_splits", 0)), 1) * M * N * 8
+    need = max(need, ll if kwargs.get("algo") == "push" else min(2 * ll, 64 << 20) if M <= 64 else 0)
     hdl = symm_mem.get_symm_mem_workspace(group, need, a.device, kind="gemm_ar")
-    calls = getattr(hdl, "_gemm_ar_calls", 0)      # per staging buffer: selects the staging half / flag bank
+    calls = getattr(hdl, "_gemm_ar_calls", 0)      # per staging buffer: selects the staging half, flag bank and tag
     hdl._gemm_ar_calls = calls + 1
-    algo = {"one_shot": 0, "two_shot": 1}.get(str(kwargs.get("algo", config.force_algo() or "")), -1)
+    want = kwargs.get("algo", config.force_algo() or "")
+    algo = _AR_ALGOS.get(str(want), -1)
     if symm_mem.capturing():
-        algo = 1                        # one-shot alternates staging halves call by call: not replayable
+        algo = 1                        # the others alternate staging halves (and tags) call by call: not replayable
+    host = getattr(hdl, "_host_ptr_array", None)
     mc = hdl.multicast_ptr or None
-    _log.log_kernel_choice("gemm_one_shot_all_reduce", f"M={M} N={N} K={K} ws={hdl.world_size} "
-                           f"exchange={('by size', 'one_shot', 'two_shot')[algo + 1]} nvls={bool(mc)}")
-    _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, hdl.signal_pad_ptrs_dev, mc, hdl.rank, hdl.world_size,
+    if _log.dump_enabled():
+        plan = (ctypes.c_int * 5)()
+        _lib.check(L.kr_gemm_ar_plan(M, N, K, ws, 1 if tf32 else 0, algo, int(kwargs.get("k_splits", 0)),
+                                     hdl.buffer_size // 1024 * 1024, 1 if host is not None else 0, plan))
+        _log.log_kernel_choice("gemm_one_shot_all_reduce", f"M={M} N={N} K={K} ws={ws} "
+                               f"exchange={('one_shot', 'two_shot', 'push')[plan[0]]} k_splits={plan[1]} "
+                               f"bn={plan[2]} ctas={plan[3]} nvls={bool(mc)}")
+    _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, host, hdl.signal_pad_ptrs_dev, mc, hdl.rank, ws,
                                  a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,
-                                 int(kwargs.get("swap_ab", -1)), algo, calls & 1, config.TILE_FLAG_BASE,
+                                 int(kwargs.get("swap_ab", -1)), algo, int(kwargs.get("k_splits", 0)),
+                                 calls & 0xFFFFFFFF, config.TILE_FLAG_BASE,
                                  hdl.signal_pad_words, hdl.buffer_size // 1024 * 1024, 1 if tf32 else 0,
                                  _lib.current_stream_ptr()))
     return out

@@ -101,8 +101,9 @@ _PROTOS = {
                                 c_int, c_int, c_int, c_uint32, c_uint32, c_ulonglong, c_ulonglong, _P]),
     "kr_gemm_rs_set_trace": (c_int, [_P, c_ulonglong]),
     "kr_rs_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P]),
-    "kr_gemm_ar_bf16": (c_int, [_P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_uint32, c_ulonglong, c_ulonglong, c_int, _P]),
+    "kr_gemm_ar_bf16": (c_int, [_P, _P, _P, _P, c_int, c_int, _P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_uint32, c_uint32, c_ulonglong, c_ulonglong, c_int, _P]),
+    "kr_gemm_ar_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_ulonglong, c_int, _P]),
     "kr_gemm_ce_producer_bf16": (c_int, [_P, c_longlong, _P, c_longlong, _P, c_longlong, c_int, c_int, c_int, c_int,
                                          c_int, _P, _P, _P]),
     "kr_tile_order_ag": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, _P]),

@@ -275,13 +275,66 @@ def test_gemm_one_shot_all_reduce(ws, M, algo):
             assert torch.equal(outs[0], outs[r])
 
 
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("M", [1, 5, 16, 64])
+@pytest.mark.parametrize("k_splits", [0, 1, 2])
+def test_gemm_all_reduce_tagged_push(ws, M, k_splits):
+    # decode exchange: {value, tag} pairs pushed into every rank's slots, summed as they land; with
+    # k_splits = 2 two CTAs per tile each multiply half of K and the slots double
+    world = EmuWorld(ws)
+    N, Kl = 1024, 256
+    g = torch.Generator().manual_seed(31)
+    for it in range(4):      # both staging halves twice: a slot's previous tag must never satisfy a wait
+        a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+        bt_s = [(0.02 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
+        full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo="push", k_splits=k_splits))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
+            assert torch.equal(outs[0], outs[r])
+
+
+@pytest.mark.parametrize("ws,M", [(2, 16), (2, 64), (4, 64), (8, 16)])
+def test_gemm_all_reduce_two_shot_split_k(ws, M):
+    world = EmuWorld(ws)
+    N, Kl = 1024, 512
+    g = torch.Generator().manual_seed(32)
+    a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+    bt_s = [(0.02 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
+    full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
+    for _ in range(3):
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo="two_shot", k_splits=2))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
+            assert torch.equal(outs[0], outs[r])
+
+
+def test_gemm_all_reduce_plan_prefers_push_for_decode_rows():
+    import ctypes
+
+    from kraken_b200.ops import lib as klib
+
+    def plan(M, N, K, ws, S=32 << 20):
+        out = (ctypes.c_int * 5)()
+        klib.check(klib.lib().kr_gemm_ar_plan(M, N, K, ws, 0, -1, 0, S, 1, out))
+        return list(out)
+
+    algo, ks, bn, ctas, swap = plan(1, 8192, 1024, 8)
+    assert algo == 2 and swap == 1 and ctas == 64 * ks
+    algo, ks, *_ = plan(256, 8192, 1024, 8, 256 << 20)
+    assert algo == 1                      # 8 MB of output: tile owners reduce
+    algo, ks, *_ = plan(1, 8192, 4096, 2)
+    assert algo == 2 and ks == 2          # long K per rank: two CTAs per tile stream the weights
+
+
 def test_gemm_all_reduce_alternating_shapes_and_algorithms():
     # consecutive calls of different shapes and exchange algorithms share one staging buffer
     ws = 4
     world = EmuWorld(ws)
     g = torch.Generator().manual_seed(10)
     for M, N, algo in [(256, 1024, "two_shot"), (16, 512, "one_shot"), (64, 1024, "two_shot"), (1, 1024, "one_shot"),
-                       (200, 520, "two_shot"), (200, 520, "one_shot")]:
+                       (1, 1024, "push"), (16, 512, "push"), (16, 512, "one_shot"), (3, 1024, "push"), (64, 512, None),
+                       (200, 520, "two_shot"), (200, 520, "one_shot"), (8, 520, "push"), (8, 520, None)]:
         a_s = [torch.randn(M, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
         bt_s = [(0.02 * torch.randn(N, 128, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
         full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))

@@ -204,8 +204,12 @@ def _all_ops(rank, ws):
         ad = torch.randn(Md, 1024, device=dev).to(torch.bfloat16)
         btd = (0.02 * torch.randn(2048, 1024, device=dev)).to(torch.bfloat16)
         gold_d = nccl_sum(ad.float() @ btd.float().t())
-        for algo in ("one_shot", "two_shot", "one_shot", "two_shot", None):
-            o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t(), **({"algo": algo} if algo else {}))
+        algos = ("one_shot", "two_shot", "one_shot", "two_shot", None)
+        if Md <= 64:
+            algos += ("push", "push", ("push", 2), "one_shot", ("push", 1), ("two_shot", 2), None, None)
+        for algo in algos:
+            kw = {} if algo is None else ({"algo": algo} if isinstance(algo, str) else {"algo": algo[0], "k_splits": algo[1]})
+            o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t(), **kw)
             assert o.dtype == torch.float32
             torch.testing.assert_close(o, gold_d, atol=5e-3, rtol=5e-3)
     ones = torch.ones(32, 32, device=dev, dtype=torch.bfloat16)
