@@ -1,6 +1,7 @@
 """Decode-shaped chain (no reference script; the shapes come from the tensor-parallel decode use
 case the reference's ops target): gemm_one_shot_all_reduce_fused with A bf16 [M, 8192/ws],
-B bf16 [8192/ws, 8192], M in {1, 16, 64, 256}, then two_shot_all_reduce_bias_rms_norm on [M, 8192].
+B bf16 [8192/ws, 8192], M in {1, 16, 64, 256}, then all-reduce + bias + RMSNorm on [M, 8192] (the
+one-shot form up to M = 64, the two-shot form beyond).
 Baselines: cuBLAS + NCCL all_reduce (fp32), and NCCL all_reduce + add + rms_norm."""
 from __future__ import annotations
 
@@ -74,7 +75,10 @@ def main():
             # the decode step this benchmark is about: GEMM + all-reduce, then the next layer's
             # all-reduce + bias + RMSNorm, back to back on one stream
             fused.gemm_one_shot_all_reduce_fused(a, b)
-            fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5)
+            if M <= 64:
+                fused.one_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5)
+            else:
+                fused.two_shot_all_reduce_bias_rms_norm(pad, x, bias, w, y, 1e-5)
 
         backends["chain_gemm_ar_then_ar_bias_norm"] = chain
         if ref is not None and ((M + 63) // 64) * (N // 64) * ws <= 2304:
