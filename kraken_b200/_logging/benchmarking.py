@@ -40,7 +40,8 @@ def _align_ranks() -> None:
 def benchmark_with_event(target_fn: Callable[[], None], warmup_iters: int = 200, benchmark_iters: int = 25,
                          profile_ranks: list[int] | None = None, flush_l2: bool = False, cuda_graph: bool = False,
                          max_over_ranks: bool = True, return_all: bool = False):
-    """Median device time of `target_fn` in microseconds (max over ranks by default)."""
+    """Median device time of `target_fn` in microseconds (max over ranks by default). With
+    ``profile_ranks`` given, those ranks also record a short profiler trace after the timed loop."""
     if cuda_graph:
         target_fn()
         torch.cuda.synchronize()
@@ -71,9 +72,41 @@ def benchmark_with_event(target_fn: Callable[[], None], warmup_iters: int = 200,
     med = lat[len(lat) // 2] if len(lat) % 2 else 0.5 * (lat[len(lat) // 2 - 1] + lat[len(lat) // 2])
     if max_over_ranks:
         med = _max_over_ranks(med)
+    if profile_ranks is not None:
+        _trace_pass(inner, profile_ranks)
     if return_all:
         return med, lat
     return med
+
+
+def _trace_pass(fn: Callable[[], None], profile_ranks: list[int], iters: int = 3) -> str | None:
+    """A few extra calls under ``torch.profiler`` on the ranks named, AFTER the timed loop, so that
+    no reported time is taken under a profiler (the reference wraps its timed loop in the profiler:
+    kraken/_logging/benchmarking.py:131-152). The trace goes to a user-supplied
+    ``trace_handler.trace_handler`` when that module is importable, else as a Chrome trace into
+    ``$KRAKEN_TRACE_DIR`` (default: the temp directory). ``NO_TRACE`` in the environment skips it.
+    Returns the path written, if any."""
+    rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+    if rank not in profile_ranks or "NO_TRACE" in os.environ:
+        return None
+    try:
+        from trace_handler import trace_handler  # user-supplied module, optional
+    except ImportError:
+        trace_handler = None
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA],
+                                on_trace_ready=trace_handler) as prof:
+        for _ in range(iters):
+            fn()
+        torch.cuda.synchronize()
+    if trace_handler is not None:
+        return None
+    import tempfile
+
+    out_dir = os.environ.get("KRAKEN_TRACE_DIR", tempfile.gettempdir())
+    os.makedirs(out_dir, exist_ok=True)
+    path = os.path.join(out_dir, f"kraken_b200_trace_rank{rank}_{os.getpid()}.json")
+    prof.export_chrome_trace(path)
+    return path
 
 
 def benchmark_with_profiler(target_fn: Callable[[], None], event_key_regex: str, warmup_iters: int = 200,

@@ -102,6 +102,29 @@ def rs_nvls() -> bool:
     return os.environ.get("KRAKEN_RS_NVLS", "0") == "1"
 
 
+def _env_float(name: str, default: float) -> float:
+    try:
+        return float(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def gemm_flops_per_s() -> float:
+    """Sustained bf16 rate of the GEMM core that sizing heuristics assume (how many comm CTAs an
+    all-gather GEMM needs to keep up). Measured on B200 under the power cap: about 1.45 PFLOP/s.
+    KRAKEN_GEMM_TFLOPS overrides (TFLOP/s)."""
+    return _env_float("KRAKEN_GEMM_TFLOPS", 1450.0) * 1e12
+
+
+def comm_cta_bytes_per_s(engine: str) -> float:
+    """What one comm CTA of an in-kernel all-gather engine moves over NVLink, as measured at 2 and 8
+    GPUs: "pull" (bulk async copies from a peer) about 15 GB/s, "push" (bulk stores to one peer)
+    about 20 GB/s, "multicast" (multimem.st from registers) about 10 GB/s. Bounded by what the CTA
+    keeps in flight over the link latency. KRAKEN_COMM_CTA_GBS_<ENGINE> overrides (GB/s)."""
+    default = {"pull": 15.0, "push": 20.0, "multicast": 10.0}[engine]
+    return _env_float("KRAKEN_COMM_CTA_GBS_" + engine.upper(), default) * 1e9
+
+
 def dump_kernel() -> bool:
     return os.environ.get("KRAKEN_DUMP_KERNEL", "0") == "1"
 

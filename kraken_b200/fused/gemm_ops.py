@@ -74,8 +74,8 @@ def _default_comm_ctas(n_local: int, ws: int) -> int:
         return config.num_comm_sms()
     if ws == 1:
         return 2
-    rate = 1.45e15 / max(1, n_local)            # bytes per second needed
-    n = int(-(-rate // 15e9))
+    rate = config.gemm_flops_per_s() / max(1, n_local)            # bytes per second needed
+    n = int(-(-rate // config.comm_cta_bytes_per_s("pull")))
     n = (n + 1) & ~1
     return max(2, min(32, n))
 
@@ -89,12 +89,12 @@ def _default_push_ctas(shard_bytes: int, ws: int, flops: float, multicast: bool)
 
     if "KRAKEN_NUM_COMM_SMS" in os.environ:
         return config.num_comm_sms()
-    t_gemm = flops / 1.45e15
+    t_gemm = flops / config.gemm_flops_per_s()
     if multicast:
         return 8           # measured at 8 GPUs: 4 starve the GEMM, 16 cost more SMs than they save (M = 2048 and 8192)
     else:
         rate = ws * shard_bytes / max(t_gemm, 1e-6)
-        n = int(-(-rate // 20e9))
+        n = int(-(-rate // config.comm_cta_bytes_per_s("push")))
     n = (n + 1) & ~1
     return max(2, min(16, n))
 

@@ -141,8 +141,8 @@ def _find_allocation(t: torch.Tensor) -> SymmAllocation | None:
         return hit
     for a in _allocations:
         if a.device == t.device and a.contains(ptr):
-            if len(_alloc_by_ptr) > 4096:
-                _alloc_by_ptr.clear()
+            while len(_alloc_by_ptr) >= 4096:                    # evict the oldest entries, keep the hot ones
+                _alloc_by_ptr.pop(next(iter(_alloc_by_ptr)))
             _alloc_by_ptr[key] = a
             return a
     return None

@@ -34,3 +34,25 @@ def test_ops_replay_under_cuda_graph():
         torch.cuda.synchronize()
         torch.testing.assert_close(out.float(), chain().float(), atol=2e-2, rtol=2e-2)
     assert ref.shape == out.shape
+
+
+def test_benchmark_harness_times_outside_the_profiler_and_traces_on_request(tmp_path, monkeypatch):
+    # profile_ranks asks for a trace: it is recorded in extra calls after the timed loop
+    from kraken_b200._logging.benchmarking import benchmark_with_event
+
+    monkeypatch.setenv("KRAKEN_TRACE_DIR", str(tmp_path))
+    monkeypatch.delenv("NO_TRACE", raising=False)
+    x = torch.randn(1 << 20, device="cuda")
+    calls = []
+
+    def fn():
+        calls.append(1)
+        x.mul_(1.0)
+
+    us = benchmark_with_event(fn, warmup_iters=3, benchmark_iters=5, profile_ranks=[0], flush_l2=True, max_over_ranks=False)
+    assert us > 0 and len(calls) == 3 + 5 + 3
+    traces = list(tmp_path.glob("kraken_b200_trace_rank0_*.json"))
+    assert len(traces) == 1 and traces[0].stat().st_size > 0
+    calls.clear()
+    us_g = benchmark_with_event(fn, warmup_iters=2, benchmark_iters=5, cuda_graph=True, max_over_ranks=False)
+    assert us_g > 0 and len(calls) == 2           # captured once after one eager call; replays do not re-enter Python
