@@ -354,6 +354,16 @@ __device__ void sync_test_body(const SyncTestParams& p, unsigned bid, unsigned n
   } else if (p.mode == 2) {
     bool ok = wait_gmem_barrier(p.flags + bid, 1u, p.sync, 24);
     if (threadIdx.x == 0) p.out[bid] = ok ? 1u : 2u;
+  } else if (p.mode >= 4) {
+    // one barrier of the pattern the caller names: bit 1 = earlier accesses, bit 0 = later accesses
+    bool ok;
+    switch (p.mode & 3) {
+      case 0: ok = symm_mem_sync<false, false>(p.pads, bid, p.rank, p.ws, p.sync, 26); break;
+      case 1: ok = symm_mem_sync<false, true>(p.pads, bid, p.rank, p.ws, p.sync, 27); break;
+      case 2: ok = symm_mem_sync<true, false>(p.pads, bid, p.rank, p.ws, p.sync, 28); break;
+      default: ok = symm_mem_sync<true, true>(p.pads, bid, p.rank, p.ws, p.sync, 29); break;
+    }
+    if (threadIdx.x == 0) p.out[bid] = ok ? 1u : 0u;
   } else {
     // Bounds-check self-test: index num_producers is checked against a limit of num_producers
     // (one past the end). In the debug build the check fails, records KR_ERR_BOUNDS and the store is
@@ -523,7 +533,8 @@ KR_API int kr_reduce_slabs(const void* slabs, void* out, int ws, int start, unsi
 }
 
 // mode 0: three symm_mem_sync patterns per block; 1: gmem arrive/wait; 2: wait that must time out;
-// 3: bounds-check self-test (out needs num_producers + 1 words).
+// 3: bounds-check self-test (out needs num_producers + 1 words); 4..7: ONE symm_mem_sync per block,
+// pattern = (mode & 2: the block accessed symmetric memory before, mode & 1: it will after).
 KR_API int kr_sync_test(uint32_t* const* pads, int rank, int ws, uint32_t* flags, uint32_t* out, int mode,
                         int num_blocks, int num_producers, cudaStream_t stream) {
   DeviceState* d = device_state();

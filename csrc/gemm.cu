@@ -9,6 +9,7 @@
 //    CTAs start on the local shard (rank pivot) and consume remote chunks as their flags appear.
 //    One launch, no copy engine, no second stream. A copy-engine feed is available as well.
 //  * copy-engine reduce-scatter producer (reference: gemm_reduce_scatter_ce_persistent.py:46-134).
+#include <deque>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -424,6 +425,8 @@ struct TmapKey {
 };
 static std::mutex g_tmap_mu;
 static std::map<TmapKey, CUtensorMap> g_tmap_cache;
+static std::deque<TmapKey> g_tmap_order;             // insertion order, for eviction
+constexpr size_t kTmapCacheEntries = 4096;
 static unsigned long long g_tmap_hits = 0, g_tmap_misses = 0;
 
 // Tensor map of a row-major matrix [rows, cols] of bf16 (elt 2) or fp32 (elt 4) elements (cols
@@ -456,8 +459,12 @@ int get_tmap(const void* ptr, unsigned long long rows, unsigned long long cols, 
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   {
     std::lock_guard<std::mutex> lk(g_tmap_mu);
-    if (g_tmap_cache.size() > 4096) g_tmap_cache.clear();
-    g_tmap_cache[key] = m;
+    // bounded: the oldest descriptors go first, so a loop over a few operands keeps hitting
+    while (g_tmap_cache.size() >= kTmapCacheEntries && !g_tmap_order.empty()) {
+      g_tmap_cache.erase(g_tmap_order.front());
+      g_tmap_order.pop_front();
+    }
+    if (g_tmap_cache.emplace(key, m).second) g_tmap_order.push_back(key);
     ++g_tmap_misses;
   }
   *out = m;

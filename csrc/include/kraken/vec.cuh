@@ -75,6 +75,10 @@ __device__ __forceinline__ void multimem_st16(void* mc_ptr, const U4& v) {
                "f"(__uint_as_float(v.w))
                : "memory");
 }
+// Broadcast store of one 64-bit word (seen whole at every destination).
+__device__ __forceinline__ void multimem_st_u64(void* mc_ptr, unsigned long long v) {
+  asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_ptr), "l"(v) : "memory");
+}
 // Broadcast +1 on a flag word in every bound device's memory.
 __device__ __forceinline__ void multimem_red_add_release_u32(uint32_t* mc_ptr, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");

@@ -20,16 +20,25 @@ HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.ab
                       "csrc", "include", "kraken", "ptx_sync.cuh")
 
 
-def symm_mem_sync(signal_pad_ptrs, block_id, rank: int, world_size: int, hasPreviousMemAccess: bool = False,
-                  hasSubsequentMemAccess: bool = False, num_blocks: int = 1) -> torch.Tensor:
-    """Launches `num_blocks` blocks that each run the three barrier patterns (F,T), (T,T), (T,F) of
-    the per-block cross-device barrier with blocks of the same id on all ranks, on the current
-    stream. `signal_pad_ptrs` is a handle (or its ``signal_pad_ptrs_dev``). Returns a uint32 tensor
-    with 1 per block whose waits all completed. The pattern arguments are accepted for signature
-    parity; a host launch has no surrounding kernel whose accesses they would order."""
+def symm_mem_sync(signal_pad_ptrs, block_id=None, rank: int = 0, world_size: int = 1,
+                  hasPreviousMemAccess: bool | None = None, hasSubsequentMemAccess: bool | None = None,
+                  num_blocks: int = 1) -> torch.Tensor:
+    """Launches `num_blocks` blocks on the current stream that each meet the blocks of the same id
+    on all ranks in the per-block cross-device barrier. With both pattern arguments left at None
+    every block runs the three patterns the library's kernels use, (F,T), (T,T), (T,F), back to
+    back (a self-test); with either given, every block runs ONE barrier of exactly that pattern
+    (hasPreviousMemAccess: release before signalling; hasSubsequentMemAccess: acquire after
+    waiting) — which, launched between two kernels of a stream, orders their symmetric-memory
+    accesses across ranks the way the device function does inside a kernel. `signal_pad_ptrs` is a
+    handle (or its ``signal_pad_ptrs_dev``); `block_id` is implied by the launch (block i uses slot
+    i) and accepted for signature parity. Returns a tensor with 1 per block whose waits completed."""
     dev_ptr = getattr(signal_pad_ptrs, "signal_pad_ptrs_dev", signal_pad_ptrs)
     out = torch.zeros(num_blocks, dtype=torch.int32, device="cuda")
-    _lib.check(_lib.lib().kr_sync_test(dev_ptr, rank, world_size, None, out.data_ptr(), 0, num_blocks, 1,
+    if hasPreviousMemAccess is None and hasSubsequentMemAccess is None:
+        mode = 0
+    else:
+        mode = 4 | (2 if hasPreviousMemAccess else 0) | (1 if hasSubsequentMemAccess else 0)
+    _lib.check(_lib.lib().kr_sync_test(dev_ptr, rank, world_size, None, out.data_ptr(), mode, num_blocks, 1,
                                        _lib.current_stream_ptr()))
     return out
 
@@ -42,7 +51,9 @@ def send_signal(handle, dst_rank: int, slot: int, value: int = 1) -> None:
 
 
 def get_flat_tid() -> str:
-    """Device-only in the reference; here: the expression user CUDA code uses."""
+    """A device function in the reference (the flattened thread index inside a block). Python has no
+    device code, so this returns the C expression for it, for user CUDA sources that are assembled
+    as text; kernels that include ``ptx_sync.cuh`` use the same expression inside ``symm_mem_sync``."""
     return "threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z)"
 
 

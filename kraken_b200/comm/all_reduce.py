@@ -24,13 +24,13 @@ def _dump(msg: str, hdl=None) -> None:
 
 
 # ---- push-style one-shot (small messages) ---------------------------------------------------------
-_PUSH_WORKSPACE_BYTES = 8 << 20      # two halves of world_size slots
+_PUSH_WORKSPACE_BYTES = 16 << 20     # four quarters (flag form even / odd calls, tagged form even / odd) of world_size slots
 
 
 def push_limit_bytes(ws: int) -> int:
     """Largest message the push-style one-shot kernels take: (ws - 1) x S leaves each rank, so the
     limit shrinks with the world size (512 KiB at 8 ranks, 2 MiB at 2)."""
-    return (_PUSH_WORKSPACE_BYTES // 2 // max(1, ws)) // 1024 * 1024
+    return (_PUSH_WORKSPACE_BYTES // 4 // max(1, ws)) // 1024 * 1024
 
 
 def push_eligible(nbytes: int, numel: int, ws: int, kwargs=None) -> bool:
@@ -41,7 +41,8 @@ def push_eligible(nbytes: int, numel: int, ws: int, kwargs=None) -> bool:
 
 
 def push_workspace(group, device):
-    """(handle, host array of signal-pad addresses, parity of this call) of the push workspace."""
+    """(handle, host array of signal-pad addresses, number of calls made on it so far) of the push
+    workspace. The call number picks the workspace half and is the tag of the tagged form."""
     import ctypes
 
     hdl = symm_mem.get_symm_mem_workspace(group, _PUSH_WORKSPACE_BYTES, device, kind="push")
@@ -50,16 +51,18 @@ def push_workspace(group, device):
         pads = hdl._host_pad_array = (ctypes.c_void_p * hdl.world_size)(*hdl.signal_pad_ptrs)
     calls = getattr(hdl, "_push_calls", 0)
     hdl._push_calls = calls + 1
-    return hdl, pads, calls & 1
+    return hdl, pads, calls & 0xFFFFFFFF
 
 
 def _push_all_reduce(inp: torch.Tensor, bias, out: torch.Tensor, group) -> None:
-    hdl, pads, parity = push_workspace(group, inp.device)
+    hdl, pads, seq = push_workspace(group, inp.device)
     bias_ptr, bias_n = _bias_args(bias, inp)
-    _dump(f"one_shot_all_reduce push numel={inp.numel()} ws={hdl.world_size} nvls={bool(hdl.multicast_ptr)}")
+    tagged = config.push_tagged_max_bytes()
+    _dump(f"one_shot_all_reduce push numel={inp.numel()} ws={hdl.world_size} nvls={bool(hdl.multicast_ptr)} "
+          f"tagged={inp.numel() * 2 <= tagged}")
     _lib.check(_lib.lib().kr_push_all_reduce(
         hdl._host_ptr_array, pads, hdl.multicast_ptr or None, hdl.rank, hdl.world_size, inp.data_ptr(), out.data_ptr(),
-        bias_ptr, bias_n, inp.numel(), parity, hdl.buffer_size, 0, _lib.current_stream_ptr()))
+        bias_ptr, bias_n, inp.numel(), seq, tagged, hdl.buffer_size, 0, _lib.current_stream_ptr()))
 
 
 def _check_bf16(t: torch.Tensor) -> None:

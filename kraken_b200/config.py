@@ -125,6 +125,13 @@ def comm_cta_bytes_per_s(engine: str) -> float:
     return _env_float("KRAKEN_COMM_CTA_GBS_" + engine.upper(), default) * 1e9
 
 
+def push_tagged_max_bytes() -> int:
+    """Messages up to this size take the tagged form of the push-style one-shot all-reduce (data and
+    a per-call tag in one 8-byte store, no barrier at all); larger ones the flag form (one barrier).
+    KRAKEN_PUSH_TAGGED_KB overrides; 0 turns the tagged form off."""
+    return _env_int("KRAKEN_PUSH_TAGGED_KB", 64) << 10
+
+
 def dump_kernel() -> bool:
     return os.environ.get("KRAKEN_DUMP_KERNEL", "0") == "1"
 

@@ -87,11 +87,12 @@ def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int, one_shot: 
     hdl, off = _scratch(symm_buf, x, group)
     bias_ptr, bias_n = _bias_args(bias, x)
     if algo == 0 and push_eligible(x.numel() * 2, x.numel(), hdl.world_size, {"algo": one_shot}):
-        ph, pads, parity = push_workspace(group, x.device)
+        ph, pads, seq = push_workspace(group, x.device)
         _dump(f"one_shot_all_reduce_bias_rms_norm push rows={rows} D={D} ws={ph.world_size} nvls={bool(ph.multicast_ptr)}")
         _lib.check(_lib.lib().kr_push_all_reduce_bias_rms_norm(
             ph._host_ptr_array, pads, ph.multicast_ptr or None, ph.rank, ph.world_size, x.data_ptr(), bias_ptr, bias_n,
-            w.data_ptr(), y.data_ptr(), rows, D, float(eps), parity, ph.buffer_size, 0, _lib.current_stream_ptr()))
+            w.data_ptr(), y.data_ptr(), rows, D, float(eps), seq, config.push_tagged_max_bytes(), ph.buffer_size, 0,
+            _lib.current_stream_ptr()))
         return
     mc = None
     if algo == 1 and hdl.multicast_ptr and config.force_algo() != "two_shot":

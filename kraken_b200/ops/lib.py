@@ -83,10 +83,10 @@ _PROTOS = {
     "kr_host_barrier": (c_uint32, [_P, c_ulonglong, c_int, c_int, c_int, c_double, c_int, c_int]),
     "kr_host_pad_nonzero": (c_ulonglong, [_P, c_ulonglong, c_int]),
     # push-style one-shot kernels (host pointer arrays)
-    "kr_push_all_reduce": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, _P, c_ulonglong, c_ulonglong, c_int, c_ulonglong,
-                                   c_uint32, _P]),
+    "kr_push_all_reduce": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, _P, c_ulonglong, c_ulonglong, c_uint32, c_ulonglong,
+                                   c_ulonglong, c_uint32, _P]),
     "kr_push_all_reduce_bias_rms_norm": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_ulonglong, _P, _P, c_int, c_int,
-                                                 c_float, c_int, c_ulonglong, c_uint32, _P]),
+                                                 c_float, c_uint32, c_ulonglong, c_ulonglong, c_uint32, _P]),
     # norm kernels
     "kr_rms_norm": (c_int, [_P, _P, _P, c_int, c_int, c_float, _P]),
     "kr_all_reduce_bias_rms_norm": (c_int, [_P, c_ulonglong, _P, c_int, c_int, _P, _P, c_ulonglong, _P, _P, c_int, c_int, c_float,

@@ -187,7 +187,7 @@ def test_push_and_pull_one_shot_agree(ws, numel, with_bias):
 
 
 @pytest.mark.parametrize("ws", [1, 2, 4, 8])
-@pytest.mark.parametrize("b,D", [(1, 5120), (3, 5120), (16, 1024), (40, 8192), (2, 64)])
+@pytest.mark.parametrize("b,D", [(1, 5120), (3, 5120), (16, 1024), (40, 8192), (2, 64), (2, 8192), (4, 4096)])
 def test_push_all_reduce_bias_rms_norm(ws, b, D):
     world = EmuWorld(ws)
     xs = _inputs(ws, (b, D), seed=33)
@@ -205,3 +205,22 @@ def test_push_all_reduce_bias_rms_norm(ws, b, D):
             world.run(lambda r: fused.one_shot_all_reduce_bias_rms_norm(pads[r], xs[r], bias, w, ys[r], 1e-5, algo=algo))
             for r in range(ws):
                 torch.testing.assert_close(ys[r].float(), expect, atol=4e-2, rtol=4e-2)
+
+
+def test_push_tagged_and_flag_forms_share_a_workspace(monkeypatch):
+    # small messages travel tagged (no barrier), larger ones behind one barrier; both forms alternate
+    # workspace halves by the same call counter and must never read each other's leftovers
+    ws, numel = 4, 4096
+    world = EmuWorld(ws)
+    pads = world.symmetric((numel,), torch.bfloat16)
+    for i, kb in enumerate([64, 0, 64, 64, 0, 0, 64, 0, 64]):
+        monkeypatch.setenv("KRAKEN_PUSH_TAGGED_KB", str(kb))
+        xs = _inputs(ws, (numel,), seed=100 + i)
+        expect = sum(x.float() for x in xs)
+        outs = [torch.empty_like(xs[r]) for r in range(ws)]
+        for o in outs:
+            _poison(o)
+        world.run(lambda r: fused.one_shot_all_reduce_bias(pads[r], xs[r], None, outs[r], algo="push"))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r].float(), expect, atol=5e-2, rtol=5e-2)
+            assert torch.equal(outs[0], outs[r])

@@ -72,3 +72,18 @@ def test_bounded_wait_reports_timeout_and_context_survives():
         kraken_b200.check_status()
     finally:
         klib.check(L.kr_set_timeout_ms(old))
+
+
+@pytest.mark.parametrize("ws", [2, 4])
+@pytest.mark.parametrize("prev,subseq", [(False, False), (False, True), (True, False), (True, True)])
+def test_symm_mem_sync_single_pattern(ws, prev, subseq):
+    # the reference's signature: one barrier of the pattern named by the two flags
+    world = EmuWorld(ws)
+    ts = world.symmetric((64,), torch.float32)
+    outs = world.run(lambda r: ptx.symm_mem_sync(symm_mem.rendezvous(ts[r]), None, r, ws, prev, subseq, num_blocks=3))
+    torch.cuda.synchronize()
+    for r in range(ws):
+        assert outs[r].tolist() == [1, 1, 1]
+        with world.rank(r):
+            hdl = symm_mem.rendezvous(ts[r])
+        assert int(hdl.get_signal_pad(r).to(torch.int64).abs().sum()) == 0      # every token consumed
