@@ -544,15 +544,38 @@ def capturing() -> bool:
         return False
 
 
+_CALL_COUNTERS = ("_push_calls", "_gemm_ar_calls", "_gemm_rs_calls", "_ag_calls")
+
+
 def reset_signal_pads(handle: SymmHandle) -> None:
-    """Recovery after a reported timeout: a wait that gave up can leave tokens behind in the
-    signal pads. Collective over the handle's group: every rank zeroes its own pad between two
-    process-group barriers (host side), after which the barrier protocol starts clean again."""
+    """Recovery after a reported timeout. A wait that gave up can leave tokens behind in the signal
+    pads, and a rank that made a call its peers did not make is one call ahead in the per-workspace
+    call counters (which pick buffer halves, flag banks and tags). Collective over the handle's
+    group, host side: between two process-group barriers every rank zeroes its own pad of the handle
+    and of every library workspace of that group, and the call counters are set to one common value
+    above every rank's (so no tag is ever reused), after which all protocols start clean again."""
     pg = handle.group.pg
     torch.cuda.synchronize()
     if pg is not None:
         dist.barrier(group=pg)
     handle.get_signal_pad(handle.rank).zero_()
+    dev_index = handle.get_signal_pad(handle.rank).device.index
+    spaces = [h for (name, dev, _kind), h in sorted(_workspaces.items(), key=lambda kv: kv[0][2])
+              if name == handle.group.name and dev == dev_index]
+    for h in spaces:
+        h.get_signal_pad(h.rank).zero_()
+    counts = [int(getattr(h, attr, 0)) for h in spaces for attr in _CALL_COUNTERS]
+    if counts:
+        top = max(counts)
+        if pg is not None:
+            on_gpu = dist.get_backend(pg) == "nccl"
+            t = torch.tensor([top], dtype=torch.int64, device=handle.get_signal_pad(handle.rank).device if on_gpu else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=pg)
+            top = int(t.item())
+        for h in spaces:
+            for attr in _CALL_COUNTERS:
+                if hasattr(h, attr):
+                    setattr(h, attr, top + 2)
     torch.cuda.synchronize()
     if pg is not None:
         dist.barrier(group=pg)
