@@ -110,11 +110,25 @@ using namespace kraken;
 
 // ---- allocation -------------------------------------------------------------------------------
 
+// Answered once per device and cached: ops ask on every call, also while a stream is being captured,
+// when nothing that touches the context (cudaFree) may run.
 KR_API int kr_symm_multicast_supported() {
+  static std::mutex mu;
+  static int cached[64];
+  static bool init = false;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  (void)cudaFree(0);
-  return multicast_supported(dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (!init) {
+    for (int& c : cached) c = -1;
+    init = true;
+  }
+  if (dev < 0 || dev >= 64) return 0;
+  if (cached[dev] < 0) {
+    (void)cudaFree(0);   // make sure the primary context exists
+    cached[dev] = multicast_supported(dev) ? 1 : 0;
+  }
+  return cached[dev];
 }
 
 // Creates this rank's block: `bytes` of data followed by `pad_bytes` of signal pad, all zeroed. The

@@ -56,3 +56,20 @@ def test_benchmark_harness_times_outside_the_profiler_and_traces_on_request(tmp_
     calls.clear()
     us_g = benchmark_with_event(fn, warmup_iters=2, benchmark_iters=5, cuda_graph=True, max_over_ranks=False)
     assert us_g > 0 and len(calls) == 2           # captured once after one eager call; replays do not re-enter Python
+
+
+def test_capability_queries_are_safe_inside_stream_capture():
+    # ops ask whether multicast is supported on every call; under capture the answer must come from
+    # a cache (anything that touches the context, like cudaFree, invalidates a capture)
+    from kraken_b200.ops import lib as klib
+
+    L = klib.lib()
+    before = L.kr_symm_multicast_supported()
+    x = torch.randn(1024, device="cuda")
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        assert L.kr_symm_multicast_supported() == before
+        y = x * 2
+    g.replay()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(y, x * 2)
