@@ -12,7 +12,7 @@ namespace kraken {
 template <int BN>
 __device__ __forceinline__ void gemm_ar_body(const GemmParams& p, unsigned bid, unsigned nb) {
   extern __shared__ unsigned char smem_raw[];
-  ArHooks h;
+  ArHooksT<(BN <= 64)> h;   // the tagged push only exists for decode rows (column tiles up to 64)
   h.bn = BN;
   gemm_mainloop<BN>(p, bid, nb, h, smem_raw);
 }

@@ -11,9 +11,9 @@ template <int BN>
 __device__ __forceinline__ void gemm_tf32_body(const GemmParams& p, unsigned bid, unsigned nb) {
   extern __shared__ unsigned char smem_raw[];
   if (p.mode == GEMM_AR) {
-    ArHooks h;
+    ArHooksT<(BN <= 64)> h;   // the tagged push only exists for decode rows (column tiles up to 64)
     h.bn = BN;
-    gemm_mainloop<BN, ArHooks, 4>(p, bid, nb, h, smem_raw);
+    gemm_mainloop<BN, ArHooksT<(BN <= 64)>, 4>(p, bid, nb, h, smem_raw);
   } else {
     PlainHooks h;
     h.bn = BN;

@@ -28,7 +28,8 @@ struct PlainHooks : HookDefaults {
 // The staging buffer is dedicated to this op. One-shot alternates between two staging halves and
 // two flag banks from call to call, and in two-shot nobody leaves before every tile it takes part
 // in is published, so neither needs an exit barrier.
-struct ArHooks : HookDefaults {
+template <bool TAGGED>
+struct ArHooksT : HookDefaults {
   int bn;
   __device__ __forceinline__ bool begin_tile(const GemmParams&, int, int, int, int) { return true; }
   __device__ __forceinline__ void add_to_chunk(const GemmParams&, int, int, int, int, uint32_t (&)[32], int) {}
@@ -38,7 +39,7 @@ struct ArHooks : HookDefaults {
     char* base;
     const int slot = p.rank * nsplit(p) + k_split;
     const size_t mn = (size_t)p.out_rows * p.out_cols;
-    if (p.ar_algo == 2) {
+    if (TAGGED && p.ar_algo == 2) {
       TileDest d{nullptr, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
       d.ll_tag = p.ll_tag;
       d.ll_off = p.ll_off + (unsigned long long)slot * mn * 8ull;
@@ -60,7 +61,7 @@ struct ArHooks : HookDefaults {
   // staging, polling each pair until it carries this call's tag. No flag, no fence: the 8-byte pair
   // is one atomic store. Slots are summed in slot order, so every rank gets identical bits.
   __device__ __forceinline__ void helper_role(const GemmParams& p, unsigned bid, unsigned nb, int, int tid) {
-    if (p.ar_algo != 2) return;
+    if (!TAGGED || p.ar_algo != 2) return;
     const int ks = nsplit(p), nslots = p.ws * ks;
     const int tiles_rc = p.tiles_r * p.tiles_c;
     const size_t mn = (size_t)p.out_rows * p.out_cols;
@@ -165,7 +166,7 @@ struct ArHooks : HookDefaults {
     return false;
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
-    if (p.ar_algo == 2) return true;   // tagged push: nothing to signal, the sums happen in helper_role
+    if (TAGGED && p.ar_algo == 2) return true;   // tagged push: nothing to signal, the sums happen in helper_role
     const int tile = tile_of(p, tr, tc);
     const int tid = q * 32 + lane;   // 0..127 over the epilogue warps
     const int ks = nsplit(p), nslots = p.ws * ks;

@@ -24,12 +24,12 @@ def _dump(msg: str, hdl=None) -> None:
 
 
 # ---- push-style one-shot (small messages) ---------------------------------------------------------
-_PUSH_WORKSPACE_BYTES = 16 << 20     # four quarters (flag form even / odd calls, tagged form even / odd) of world_size slots
+_PUSH_WORKSPACE_BYTES = 64 << 20     # four quarters (flag form even / odd calls, tagged form even / odd) of world_size slots
 
 
 def push_limit_bytes(ws: int) -> int:
     """Largest message the push-style one-shot kernels take: (ws - 1) x S leaves each rank, so the
-    limit shrinks with the world size (512 KiB at 8 ranks, 2 MiB at 2)."""
+    limit shrinks with the world size (2 MiB at 8 ranks, 8 MiB at 2); beyond it the one-shot ops pull."""
     return (_PUSH_WORKSPACE_BYTES // 4 // max(1, ws)) // 1024 * 1024
 
 
