@@ -64,7 +64,7 @@ def main():
             "nccl_add_norm": nccl_norm,
         }
         if args.variants:
-            for algo in ("push", "one_shot", "two_shot"):
+            for algo in ("push", "push_two_shot", "one_shot", "two_shot"):
                 for ks in (1, 2):
                     if algo == "one_shot" and ks == 2:
                         continue

@@ -41,7 +41,7 @@ int launch_gemm_ar(int bn, const GemmParams& p, unsigned nb, cudaStream_t stream
 }
 
 // What one call does: which operand sits on the 128-row side, the column tile, the exchange
-// algorithm (0 one-shot pull, 1 two-shot, 2 tagged push) and the number of K splits, picked by a
+// algorithm (0 one-shot pull, 1 two-shot, 2 tagged push, 3 tagged two-shot) and the number of K splits, picked by a
 // small cost model (seconds). Splitting K puts more CTAs on the weight stream but multiplies the
 // partial sums that cross NVLink. algo / k_splits: -1 / 0 = choose; a given value is kept if valid.
 struct ArPlan {
@@ -68,10 +68,16 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
   auto ks_ok = [&](int ks) { return ks == 1 || ((unsigned)(pl.tiles * ks) <= cap && 2 * ks <= num_kb); };
   auto ll_ok = [&](int ks) { return pl.swap && host_ptrs && ws <= 8 && (unsigned long long)ws * ks * mn * 8 <= S / 8; };
   auto two_ok = [&](int ks) { return (unsigned long long)(ws * ks + 1) * mn4 <= S / 2; };
+  // tagged two-shot: per slot the packed tiles of one owner, then the [M][N] tagged results
+  const unsigned long long slot_pairs = (unsigned long long)((pl.tiles + ws - 1) / ws) * bn * kBM;
+  auto tag2_ok = [&](int ks) {
+    return pl.swap && host_ptrs && ws <= 8 && N % 4 == 0 && ((unsigned long long)ws * ks * slot_pairs + mn) * 8 <= S / 8;
+  };
   auto t_main = [&](int ks) { const double a1 = cta_bytes / ks / 80e9, a2 = all_bytes / 6.5e12; return a1 > a2 ? a1 : a2; };
   auto t_xfer = [&](int al, int ks) {
     // fixed costs as measured on top of the plain GEMM of the same shape: flag round trips of the
     // one- and two-shot forms against none for the tagged push
+    if (al == 3) return 3e-6 + (double)(ks + 1) * (ws - 1) / ws * mn * 8 / 400e9;
     if (al == 2) return 1e-6 + (double)ks * (ws - 1) * mn * 8 / 400e9;
     if (al == 1) return 11e-6 + (double)(ks + 1) * (ws - 1) / ws * mn4 / 600e9;
     return 9e-6 + (double)(ws - 1) * mn4 / 400e9;
@@ -80,7 +86,7 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
   pl.ks = 1;
   while (k_splits > 1 && !ks_ok(k_splits)) --k_splits;   // a requested split count is an upper bound
   double best = 1e30;
-  for (int al = 0; al <= 2; ++al) {
+  for (int al = 0; al <= 3; ++al) {
     if (algo >= 0 && al != algo) continue;
     if (algo < 0 && al == 0 && (unsigned long long)(ws - 1) * mn4 > (1ull << 20)) continue;
     for (int ks = 1; ks <= 4; ++ks) {
@@ -89,6 +95,7 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
       if (al == 0 && (ks != 1 || mn4 > S / 8)) continue;
       if (al == 1 && !two_ok(ks)) continue;
       if (al == 2 && !ll_ok(ks)) continue;
+      if (al == 3 && !tag2_ok(ks)) continue;
       const double t = t_main(ks) + t_xfer(al, ks);
       if (t < best) { best = t; pl.algo = al; pl.ks = ks; }
     }
@@ -104,7 +111,7 @@ using namespace kraken;
 // table; bufs_host: the same addresses in host memory, or nullptr), DEDICATED to this op (nothing
 // else may write it between calls, and it must have been all zero before its first use).
 // out[M, N] fp32 = sum_r a_r[M, K_local] * bt_r[N, K_local]^T.
-// algo: 0 one-shot pull, 1 two-shot, 2 tagged push, -1 by size. k_splits: parts the K range is cut
+// algo: 0 one-shot pull, 1 two-shot, 2 tagged push, 3 tagged two-shot, -1 by size. k_splits: parts the K range is cut
 // into (more CTAs streaming the weights), 0 = chosen here. call_seq: the number of calls made on
 // this staging buffer so far; every rank passes the same value.
 // Needs staging_bytes >= 8*M*N*4 (one-shot), >= 2*(ws*k_splits+1)*M*N*4 (two-shot); the tagged push
@@ -117,7 +124,7 @@ KR_API int kr_gemm_ar_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
   DeviceState* d = device_state();
   if (!d) return KR_FAIL_CUDA;
   KR_REQUIRE(ws >= 1 && rank >= 0 && rank < ws, "bad rank/world size");
-  KR_REQUIRE(algo >= -1 && algo <= 2 && k_splits >= 0 && k_splits <= 8, "bad algorithm or split count");
+  KR_REQUIRE(algo >= -1 && algo <= 3 && k_splits >= 0 && k_splits <= 8, "bad algorithm or split count");
   GemmParams p;
   memset(&p, 0, sizeof(p));
   ArPlan pl;
@@ -163,9 +170,13 @@ KR_API int kr_gemm_ar_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
   if (algo == 0) {
     p.stage_off = odd ? S / 8 : 0;
     p.flag_base = flag_base + (odd ? 50000u : 0u);
-  } else if (algo == 2) {
+  } else if (algo == 2 || algo == 3) {
     p.ll_off = S / 4 + (odd ? S / 8 : 0);
     p.ll_tag = call_seq % 0x7fffffffu + 1u;      // never 0, and never the tag this region saw two calls ago
+    if (algo == 3) {
+      p.ll_slot_pairs = (unsigned long long)((tiles + ws - 1) / ws) * bn * kBM;
+      p.ll_res_off = p.ll_off + (unsigned long long)ws * best_ks * p.ll_slot_pairs * 8;
+    }
   } else {
     p.part_off = S / 2;
     p.res_off = S / 2 + (unsigned long long)ws * best_ks * mn4;
@@ -179,7 +190,7 @@ KR_API int kr_gemm_ar_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
   return launch_gemm(bn, p, nb, stream);
 }
 
-// What kr_gemm_ar_bf16 picks for a shape: out[0] = algorithm (0 one-shot, 1 two-shot, 2 tagged push),
+// What kr_gemm_ar_bf16 picks for a shape: out[0] = algorithm (0 one-shot, 1 two-shot, 2 tagged push, 3 tagged two-shot),
 // out[1] = K splits, out[2] = column tile, out[3] = CTAs, out[4] = 1 when the weights sit on the
 // 128-row side. For logs and tests; no launch.
 KR_API int kr_gemm_ar_plan(int M, int N, int K, int ws, int in_fp32, int algo, int k_splits,

@@ -106,6 +106,10 @@ struct alignas(64) GemmParams {
   // [ws * k_splits][M][N] of {fp32 value, tag} pairs inside every rank's staging buffer
   uint32_t ll_tag;
   unsigned long long ll_off;
+  // AR, tagged two-shot: pairs per partial slot at a tile's owner (tiles of one owner, packed), and
+  // the byte offset of the [M][N] array of tagged results inside every rank's staging buffer
+  unsigned long long ll_slot_pairs;
+  unsigned long long ll_res_off;
   // RS
   int slab_rows;             // M / ws
   int rs_algo;               // 0: push, owner reduces in its epilogue; 1: pull; 2: scatter (push + reducer warps)
@@ -203,6 +207,11 @@ struct TileDest {
   // buffer (GemmParams::peer_buf) instead of to `base`.
   uint32_t ll_tag = 0;
   unsigned long long ll_off = 0;
+  // The pair of element (row, column) sits at ll_off + 8 * ((row - ll_row0) * ll_ld + (column - ll_col0));
+  // ll_ld == 0 means the destination's own `ld`. ll_dst >= 0: only that rank receives it.
+  int ll_row0 = 0, ll_col0 = 0;
+  long long ll_ld = 0;
+  int ll_dst = -1;
 };
 
 // Epilogue of one tile, run by the four epilogue warps: TMEM -> registers -> (hook: add peers'
@@ -238,9 +247,15 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
           const int drow = dst.col0 + c0 + j;
           if (drow < dst.rows) {
             if (dst.ll_tag != 0) {
-              const unsigned long long o = dst.ll_off + 8ull * ((unsigned long long)drow * dst.ld + dcol);
+              const unsigned long long o =
+                  dst.ll_off + 8ull * ((unsigned long long)(drow - dst.ll_row0) * (dst.ll_ld ? dst.ll_ld : dst.ld) +
+                                       (unsigned long long)(dcol - dst.ll_col0));
               const unsigned long long v = ((unsigned long long)dst.ll_tag << 32) | r[j];
-              for (int d = 0; d < p.ws; ++d) st_relaxed_sys_u64((char*)p.peer_buf[d] + o, v);
+              if (dst.ll_dst >= 0) {
+                st_relaxed_sys_u64((char*)p.peer_buf[dst.ll_dst] + o, v);
+              } else {
+                for (int d = 0; d < p.ws; ++d) st_relaxed_sys_u64((char*)p.peer_buf[d] + o, v);
+              }
             } else if (p.out_fp32) ((float*)dst.base)[(long long)drow * dst.ld + dcol] = __uint_as_float(r[j]);
             else ((__nv_bfloat16*)dst.base)[(long long)drow * dst.ld + dcol] = __float2bfloat16(__uint_as_float(r[j]));
           }

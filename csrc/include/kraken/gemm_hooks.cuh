@@ -45,6 +45,19 @@ struct ArHooksT : HookDefaults {
       d.ll_off = p.ll_off + (unsigned long long)slot * mn * 8ull;
       return d;
     }
+    if (TAGGED && p.ar_algo == 3) {
+      // tagged two-shot: the pairs go to the tile's owner only, into the slot's packed array of
+      // that owner's tiles (tile-local coordinates, 128 pairs per row)
+      const int tile = tile_of(p, tr, tc);
+      TileDest d{nullptr, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
+      d.ll_tag = p.ll_tag;
+      d.ll_off = p.ll_off + ((unsigned long long)slot * p.ll_slot_pairs + (unsigned long long)(tile / p.ws) * bn * kBM) * 8ull;
+      d.ll_row0 = tc * bn;
+      d.ll_col0 = tr * kBM;
+      d.ll_ld = kBM;
+      d.ll_dst = tile % p.ws;
+      return d;
+    }
     if (p.ar_algo == 0) {
       base = (char*)p.bufs[p.rank] + p.stage_off;
     } else {
@@ -54,6 +67,94 @@ struct ArHooksT : HookDefaults {
     return TileDest{base, (long long)p.out_cols, tr * kBM, tc * bn, p.out_rows, p.out_cols, nullptr};
   }
   __device__ __forceinline__ int nsplit(const GemmParams& p) const { return p.k_splits > 1 ? p.k_splits : 1; }
+  // Polls `nsl` slots (stride `stride` bytes) of four consecutive tagged pairs at `src` until all
+  // carry the tag and adds the values, slot after slot, into acc. False when the wait gave up.
+  __device__ __forceinline__ bool poll_quad(const GemmParams& p, const char* src, size_t stride, int nsl, float (&acc)[4]) {
+    for (int s0 = 0; s0 < nsl; s0 += 4) {
+      unsigned long long v[4][4];
+      const bool ok = spin_until(
+          [&] {
+            bool all = true;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              if (s0 + k < nsl) {
+                const char* q = src + (size_t)(s0 + k) * stride;
+                ld_relaxed_sys_u64x2(q, v[k][0], v[k][1]);
+                ld_relaxed_sys_u64x2(q + 16, v[k][2], v[k][3]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) all = all && (uint32_t)(v[k][e] >> 32) == p.ll_tag;
+              }
+            return all;
+          },
+          p.sync, make_status(KR_ERR_TIMEOUT_SIGNAL, 53, 0, blockIdx.x));
+      if (!ok) return false;
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (s0 + k < nsl) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[e] += __uint_as_float((uint32_t)v[k][e]);
+        }
+    }
+    return true;
+  }
+  // Tagged two-shot (out_cols % 4 == 0): the epilogue sent each partial tile, as tagged pairs, to the
+  // tile's owner (tile % ws) only. After its last tile every CTA walks its work items again: for a
+  // tile this rank owns it sums its share of the tile over all slots as the pairs land, writes the
+  // result and publishes it, tagged again, into every rank's result array (one multimem.st per
+  // pair, or ws - 1 stores); for any other tile it polls its own result array and copies the values
+  // out. All ranks walk the same items in the same order and no CTA waits before its own pairs are
+  // out, so every wait is for data whose producer waits for nothing later: no cycle.
+  __device__ __forceinline__ void two_shot_tagged(const GemmParams& p, unsigned bid, unsigned nb, int tid) {
+    const int ks = nsplit(p), nslots = p.ws * ks;
+    const int tiles_rc = p.tiles_r * p.tiles_c;
+    const char* mine = (const char*)p.peer_buf[p.rank];
+    const unsigned long long tagw = (unsigned long long)p.ll_tag << 32;
+    for (int t = (int)bid; t < tiles_rc * ks; t += (int)nb) {
+      const int split = t / tiles_rc;
+      int tr, tc;
+      tile_coords(p, t - split * tiles_rc, tr, tc);
+      const int tile = tile_of(p, tr, tc), owner = tile % p.ws;
+      int r_lo, r_n, c_lo, c_n;
+      region(p, tr, tc, r_lo, r_n, c_lo, c_n);
+      const int r_full = r_n;
+      if (r_lo + r_n > p.out_rows) r_n = p.out_rows - r_lo;
+      if (r_n <= 0) continue;
+      const int nq = r_n * c_n / 4;
+      const int lo = (int)((long long)nq * split / ks), hi = (int)((long long)nq * (split + 1) / ks);
+      for (int qd = lo + tid; qd < hi; qd += kGemmThreads) {
+        const int i = qd * 4;
+        const int lr = i / c_n, lc = i % c_n;
+        const int rr = r_lo + lr, cc = c_lo + lc;
+        if (cc >= p.out_cols) continue;
+        const size_t res = p.ll_res_off + ((size_t)rr * p.out_cols + cc) * 8;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (owner == p.rank) {
+          const char* src = mine + p.ll_off + ((size_t)(tile / p.ws) * r_full * c_n + (size_t)lr * c_n + lc) * 8;
+          if (!poll_quad(p, src, (size_t)p.ll_slot_pairs * 8, nslots, acc)) return;
+          if (p.mc_ptr != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) multimem_st_u64((char*)p.mc_ptr + res + 8 * e, tagw | __float_as_uint(acc[e]));
+          } else {
+            for (int s = 1; s < p.ws; ++s) {
+              int peer = p.rank + s;
+              if (peer >= p.ws) peer -= p.ws;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) st_relaxed_sys_u64((char*)p.peer_buf[peer] + res + 8 * e, tagw | __float_as_uint(acc[e]));
+            }
+          }
+        } else {
+          if (!poll_quad(p, mine + res, 0, 1, acc)) return;
+        }
+        float* o = (float*)p.out + (size_t)rr * p.ldo + cc;
+        if ((((uintptr_t)o) & 15) == 0) {
+          *(float4*)o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = acc[e];
+        }
+      }
+    }
+  }
   // Tagged push: the epilogue has already written this CTA's partial tiles, as {value, tag} pairs,
   // into slot [rank * splits + split] of every rank's staging. Once all of this CTA's tiles are out
   // (so that no CTA ever waits while it still owes a peer data), the six pipeline warps sum, for
@@ -61,7 +162,11 @@ struct ArHooksT : HookDefaults {
   // staging, polling each pair until it carries this call's tag. No flag, no fence: the 8-byte pair
   // is one atomic store. Slots are summed in slot order, so every rank gets identical bits.
   __device__ __forceinline__ void helper_role(const GemmParams& p, unsigned bid, unsigned nb, int, int tid) {
-    if (!TAGGED || p.ar_algo != 2) return;
+    if (!TAGGED || p.ar_algo < 2) return;
+    if (p.ar_algo == 3) {
+      two_shot_tagged(p, bid, nb, tid);
+      return;
+    }
     const int ks = nsplit(p), nslots = p.ws * ks;
     const int tiles_rc = p.tiles_r * p.tiles_c;
     const size_t mn = (size_t)p.out_rows * p.out_cols;
@@ -166,7 +271,7 @@ struct ArHooksT : HookDefaults {
     return false;
   }
   __device__ __forceinline__ bool after_store(const GemmParams& p, int tr, int tc, int q, int lane) {
-    if (TAGGED && p.ar_algo == 2) return true;   // tagged push: nothing to signal, the sums happen in helper_role
+    if (TAGGED && p.ar_algo >= 2) return true;   // tagged forms: nothing to signal, the sums happen in helper_role
     const int tile = tile_of(p, tr, tc);
     const int tid = q * 32 + lane;   // 0..127 over the epilogue warps
     const int ks = nsplit(p), nslots = p.ws * ks;

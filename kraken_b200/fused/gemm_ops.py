@@ -230,7 +230,7 @@ def all_gather_matmul(a_shared: torch.Tensor, b: torch.Tensor, a_out: torch.Tens
     return a_out, c
 
 
-_AR_ALGOS = {"one_shot": 0, "two_shot": 1, "push": 2}
+_AR_ALGOS = {"one_shot": 0, "two_shot": 1, "push": 2, "push_two_shot": 3}
 
 
 def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torch.Tensor:
@@ -242,13 +242,15 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     partial tile goes to the own staging, a flag to every peer, and every rank sums the tile from
     all ranks (in the NVSwitch when the staging buffer has a multicast mapping); "two_shot" (larger
     outputs) — tile owner t % ws receives all partials, sums them in rank order and publishes the
-    result, which moves ws/2 times fewer bytes. Small M also splits K over several CTAs per tile so
+    result, which moves ws/2 times fewer bytes; "push_two_shot" — the two-shot exchange with tagged
+    pairs instead of flags in both directions (decode rows at larger world sizes, where pushing
+    every partial to every rank is too many bytes). Small M also splits K over several CTAs per tile so
     that more SMs stream the weights; the splits are extra slots of the same exchange. The launcher
     picks exchange and split count by a cost model. Every rank gets identical bits. Decode-sized M
     puts the weights on the 128-row side of the MMA. bf16 operands use the bf16 tensor-core path;
     fp32 x fp32 operands are multiplied as tf32 (what ``tl.dot`` does for the reference's fp32
     tests); anything else is cast to bf16.
-    kwargs: group, swap_ab, algo="push"|"one_shot"|"two_shot", k_splits=1..4."""
+    kwargs: group, swap_ab, algo="push"|"push_two_shot"|"one_shot"|"two_shot", k_splits=1..4."""
     group = kwargs.get("group")
     if a.device.type != "cuda":
         return ref.gemm_all_reduce(a, b, group)
@@ -275,6 +277,8 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
     # it is asked for, and up to 64 MB so that the cost model may pick it for decode-sized outputs
     ll = 8 * ws * max(int(kwargs.get("k_splits", 0)), 1) * M * N * 8
     need = max(need, ll if kwargs.get("algo") == "push" else min(2 * ll, 64 << 20) if M <= 64 else 0)
+    if kwargs.get("algo") == "push_two_shot":       # (splits + 1) arrays of M x N pairs, slots padded to whole tiles
+        need = max(need, 8 * (max(int(kwargs.get("k_splits", 0)), 1) + 2) * max(M, 16) * N * 8)
     hdl = symm_mem.get_symm_mem_workspace(group, need, a.device, kind="gemm_ar")
     calls = getattr(hdl, "_gemm_ar_calls", 0)      # per staging buffer: selects the staging half, flag bank and tag
     hdl._gemm_ar_calls = calls + 1
@@ -289,7 +293,7 @@ def gemm_one_shot_all_reduce(a: torch.Tensor, b: torch.Tensor, **kwargs) -> torc
         _lib.check(L.kr_gemm_ar_plan(M, N, K, ws, 1 if tf32 else 0, algo, int(kwargs.get("k_splits", 0)),
                                      hdl.buffer_size // 1024 * 1024, 1 if host is not None else 0, plan))
         _log.log_kernel_choice("gemm_one_shot_all_reduce", f"M={M} N={N} K={K} ws={ws} "
-                               f"exchange={('one_shot', 'two_shot', 'push')[plan[0]]} k_splits={plan[1]} "
+                               f"exchange={('one_shot', 'two_shot', 'push', 'push_two_shot')[plan[0]]} k_splits={plan[1]} "
                                f"bn={plan[2]} ctas={plan[3]} nvls={bool(mc)}")
     _lib.check(L.kr_gemm_ar_bf16(hdl.buffer_ptrs_dev, host, hdl.signal_pad_ptrs_dev, mc, hdl.rank, ws,
                                  a2.data_ptr(), lda, bt.data_ptr(), ldb, out.data_ptr(), N, M, N, K,

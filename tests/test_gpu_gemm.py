@@ -277,6 +277,25 @@ def test_gemm_one_shot_all_reduce(ws, M, algo):
 
 @pytest.mark.parametrize("ws", [2, 4, 8])
 @pytest.mark.parametrize("M", [1, 5, 16, 64])
+@pytest.mark.parametrize("k_splits", [0, 2])
+def test_gemm_all_reduce_tagged_two_shot(ws, M, k_splits):
+    # partial tiles travel tagged to the tile's owner only; the owner publishes tagged results
+    world = EmuWorld(ws)
+    N, Kl = 1024, 256
+    g = torch.Generator().manual_seed(41)
+    for it in range(4):
+        a_s = [torch.randn(M, Kl, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
+        bt_s = [(0.02 * torch.randn(N, Kl, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]
+        full = sum(a.float() @ bt.float().t() for a, bt in zip(a_s, bt_s))
+        outs = world.run(lambda r: fused.gemm_one_shot_all_reduce_fused(a_s[r], bt_s[r].t(), algo="push_two_shot",
+                                                                        k_splits=k_splits))
+        for r in range(ws):
+            torch.testing.assert_close(outs[r], full, atol=2e-3, rtol=2e-3)
+            assert torch.equal(outs[0], outs[r])
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+@pytest.mark.parametrize("M", [1, 5, 16, 64])
 @pytest.mark.parametrize("k_splits", [0, 1, 2])
 def test_gemm_all_reduce_tagged_push(ws, M, k_splits):
     # decode exchange: {value, tag} pairs pushed into every rank's slots, summed as they land; with
@@ -333,7 +352,8 @@ def test_gemm_all_reduce_alternating_shapes_and_algorithms():
     world = EmuWorld(ws)
     g = torch.Generator().manual_seed(10)
     for M, N, algo in [(256, 1024, "two_shot"), (16, 512, "one_shot"), (64, 1024, "two_shot"), (1, 1024, "one_shot"),
-                       (1, 1024, "push"), (16, 512, "push"), (16, 512, "one_shot"), (3, 1024, "push"), (64, 512, None),
+                       (1, 1024, "push"), (16, 512, "push"), (16, 512, "push_two_shot"), (16, 512, "one_shot"), (3, 1024, "push"),
+                       (3, 1024, "push_two_shot"), (64, 512, None), (64, 512, "push_two_shot"),
                        (200, 520, "two_shot"), (200, 520, "one_shot"), (8, 520, "push"), (8, 520, None)]:
         a_s = [torch.randn(M, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(ws)]
         bt_s = [(0.02 * torch.randn(N, 128, generator=g)).to(torch.bfloat16).cuda() for _ in range(ws)]

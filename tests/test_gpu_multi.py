@@ -206,7 +206,8 @@ def _all_ops(rank, ws):
         gold_d = nccl_sum(ad.float() @ btd.float().t())
         algos = ("one_shot", "two_shot", "one_shot", "two_shot", None)
         if Md <= 64:
-            algos += ("push", "push", ("push", 2), "one_shot", ("push", 1), ("two_shot", 2), None, None)
+            algos += ("push", "push", ("push", 2), "one_shot", ("push", 1), ("two_shot", 2), None, None,
+                      "push_two_shot", ("push_two_shot", 2), "push", "push_two_shot")
         for algo in algos:
             kw = {} if algo is None else ({"algo": algo} if isinstance(algo, str) else {"algo": algo[0], "k_splits": algo[1]})
             o = fused.gemm_one_shot_all_reduce_fused(ad, btd.t(), **kw)
