@@ -1,9 +1,12 @@
 // Fused GEMM -> all-reduce for decode shapes (reference:
-// kraken/fused/gemm_one_shot_all_reduce_fused.py:106-178): the single-CTA tcgen05 main loop with the
-// exchange hooks of gemm_hooks.cuh — fp32 partial tile to a staging buffer, per-tile flags to the
-// peers, then a one-shot sum (in the NVSwitch with multimem.ld_reduce, or ws peer loads) or a
-// two-shot exchange by tile owner. Kernels of their own, so that the exchange code does not share a
-// register allocation with the other GEMM modes.
+// kraken/fused/gemm_one_shot_all_reduce_fused.py:106-178): the single-CTA tcgen05 main loop, with K
+// optionally split over several CTAs per tile, and the exchange hooks of gemm_hooks.cuh. Four
+// exchanges: fp32 partial tiles behind per-tile flags (one-shot: summed in the NVSwitch with
+// multimem.ld_reduce or from ws peer loads; two-shot: by tile owner), or partial elements that carry
+// a per-call tag in the same 8-byte store and need no flag at all (pushed to every rank, or to the
+// tile owner with tagged results coming back). The launcher picks exchange and split count by a
+// cost model. Kernels of their own, so that the exchange code does not share a register allocation
+// with the other GEMM modes.
 #include "kraken/gemm_host.h"
 #include "kraken/gemm_hooks.cuh"
 
@@ -88,7 +91,10 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
   double best = 1e30;
   for (int al = 0; al <= 3; ++al) {
     if (algo >= 0 && al != algo) continue;
-    if (algo < 0 && al == 0 && (unsigned long long)(ws - 1) * mn4 > (1ull << 20)) continue;
+    // flag forms: above 2 ranks one-shot pull traffic grows with ws - 1, so large outputs go two-shot;
+    // at 2 ranks both move the same bytes and one-shot has one flag hop less (measured faster at every M)
+    if (algo < 0 && al == 0 && ws > 2 && (unsigned long long)(ws - 1) * mn4 > (1ull << 20)) continue;
+    if (algo < 0 && al == 1 && ws == 2 && mn4 <= S / 8) continue;
     for (int ks = 1; ks <= 4; ++ks) {
       if (k_splits > 0 && ks != k_splits) continue;
       if (!ks_ok(ks)) continue;

@@ -16,18 +16,23 @@ struct PlainHooks : HookDefaults {
   __device__ __forceinline__ bool after_store(const GemmParams&, int, int, int, int) { return true; }
 };
 
-// GEMM -> all-reduce (decode). Two exchange algorithms behind the same main loop:
-//  * one-shot (small M): the fp32 partial tile goes to the rank's OWN staging, a flag goes to
+// GEMM -> all-reduce (decode). Exchanges behind the same main loop (GemmParams::ar_algo):
+//  0 one-shot (small outputs): the fp32 partial tile goes to the rank's OWN staging, a flag goes to
 //    every peer, and every rank sums the tile from all ranks (in-switch with multimem.ld_reduce
 //    when the staging buffer has a multicast mapping, else ws peer loads in rank order).
-//  * two-shot (larger M): tile t belongs to rank t % ws. Every rank stores its partial tile into
-//    the OWNER's staging slot [src]; the owner sums the ws slots from its own memory (rank order,
-//    so every rank receives identical bits), writes the result into every rank's result buffer
-//    (one multimem.st, or ws-1 peer stores) and raises "published" flags; the others copy the tile
-//    out. NVLink bytes per rank drop from (ws-1)·M·N·4 to about 2·(ws-1)/ws·M·N·4.
-// The staging buffer is dedicated to this op. One-shot alternates between two staging halves and
-// two flag banks from call to call, and in two-shot nobody leaves before every tile it takes part
-// in is published, so neither needs an exit barrier.
+//  1 two-shot (large outputs): tile t belongs to rank t % ws. Every rank stores its partial tile into
+//    the OWNER's staging slot [src]; the owner sums the slots from its own memory (slot order, so
+//    every rank receives identical bits), writes the result into every rank's result buffer (one
+//    multimem.st, or ws-1 peer stores) and raises "published" flags; the others copy the tile out.
+//    NVLink bytes per rank drop from (ws-1)·M·N·4 to about 2·(ws-1)/ws·M·N·4.
+//  2 tagged push and 3 tagged two-shot (TAGGED kernels: decode rows, transposed tiles): the same
+//    two data flows without any flag — every partial element travels with the call's tag in one
+//    8-byte store and the reader polls the pairs; the sums happen after the CTA's last tile, in
+//    helper_role. See the comments at helper_role and two_shot_tagged.
+// With K split over several CTAs per tile (k_split), every split is one more slot of the exchange.
+// The staging buffer is dedicated to this op. One-shot and the tagged forms alternate between two
+// staging regions (and flag banks) from call to call, and in two-shot nobody leaves before every
+// tile it takes part in is published, so none needs an exit barrier.
 template <bool TAGGED>
 struct ArHooksT : HookDefaults {
   int bn;
