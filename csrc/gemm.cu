@@ -287,8 +287,13 @@ __device__ __forceinline__ void ag_mc_cta(const GemmParams& p, unsigned comm_id,
     ok = __syncthreads_and(ok ? 1 : 0) != 0;
     if (!ok) break;
     const unsigned char* src = base_ptr + (size_t)slot * kAgPiece;
-    for (uint32_t v = threadIdx.x; v < bytes / 16; v += blockDim.x)
-      multimem_st16(mc_out + off + (size_t)v * 16, *(const U4*)(src + (size_t)v * 16));
+    if (p.ag_mc_weak) {
+      for (uint32_t v = threadIdx.x; v < bytes / 16; v += blockDim.x)
+        multimem_st16_weak(mc_out + off + (size_t)v * 16, *(const U4*)(src + (size_t)v * 16));
+    } else {
+      for (uint32_t v = threadIdx.x; v < bytes / 16; v += blockDim.x)
+        multimem_st16(mc_out + off + (size_t)v * 16, *(const U4*)(src + (size_t)v * 16));
+    }
     __syncthreads();                                   // every thread has read the slot and issued its stores
     if (threadIdx.x == 0) {
       const size_t jn = j + kAgSlots;
@@ -729,6 +734,8 @@ KR_API int kr_ag_gemm_bf16(void* const* bufs, uint32_t* const* pads, const void*
       KR_REQUIRE(mc_flags != nullptr, "multicast push needs the multicast address of the flags");
       p.ag_mc_out = mc_out;
       p.ag_mc_flags = mc_flags;
+      static const int weak = [] { const char* e = getenv("KRAKEN_AG_MC_WEAK"); return (e && e[0] == '1') ? 1 : 0; }();
+      p.ag_mc_weak = weak;
     }
   }
   p.pivot_r = (rank * shard_rows) / kBM;   // start on (or next to) the local shard

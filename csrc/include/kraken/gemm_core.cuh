@@ -88,6 +88,7 @@ struct alignas(64) GemmParams {
   int ag_tiles_per_shard;    // row tiles (of this kernel's tile height) per shard, for ag_chunk_major
   void* ag_mc_out;           // multicast address of the gathered buffer (multicast push) or nullptr
   uint32_t* ag_mc_flags;     // multicast address of this call's chunk flags (multicast push)
+  int ag_mc_weak;            // 1: the shard goes out with weak multimem stores (ordered by the flag's release)
   int ag_push;               // 1: every rank pushes its shard into the peers' gathered buffers (comm CTAs)
   int ag_entry_barrier;      // push into a caller-owned symmetric a_out: wait until every rank has entered
   unsigned long long ag_out_off;   // push: byte offset of the gathered buffer inside bufs[r]

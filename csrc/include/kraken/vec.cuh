@@ -75,6 +75,13 @@ __device__ __forceinline__ void multimem_st16(void* mc_ptr, const U4& v) {
                "f"(__uint_as_float(v.w))
                : "memory");
 }
+// The same as a weak store: no ordering of its own, made visible by a later release (a flag).
+__device__ __forceinline__ void multimem_st16_weak(void* mc_ptr, const U4& v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
 // Broadcast store of one 64-bit word (seen whole at every destination).
 __device__ __forceinline__ void multimem_st_u64(void* mc_ptr, unsigned long long v) {
   asm volatile("multimem.st.relaxed.sys.global.u64 [%0], %1;" ::"l"(mc_ptr), "l"(v) : "memory");
