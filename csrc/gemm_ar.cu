@@ -178,6 +178,7 @@ KR_API int kr_gemm_ar_bf16(void* const* bufs, void* const* bufs_host, uint32_t* 
     p.flag_base = flag_base + (odd ? 50000u : 0u);
   } else if (algo == 2 || algo == 3) {
     p.ll_off = S / 4 + (odd ? S / 8 : 0);
+    p.ll_end = p.ll_off + S / 8;
     p.ll_tag = call_seq % 0x7fffffffu + 1u;      // never 0, and never the tag this region saw two calls ago
     if (algo == 3) {
       p.ll_slot_pairs = (unsigned long long)((tiles + ws - 1) / ws) * bn * kBM;

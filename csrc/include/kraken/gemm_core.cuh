@@ -111,6 +111,7 @@ struct alignas(64) GemmParams {
   // the byte offset of the [M][N] array of tagged results inside every rank's staging buffer
   unsigned long long ll_slot_pairs;
   unsigned long long ll_res_off;
+  unsigned long long ll_end;        // byte offset one past this call's tagged region (bounds checks of the debug build)
   // RS
   int slab_rows;             // M / ws
   int rs_algo;               // 0: push, owner reduces in its epilogue; 1: pull; 2: scatter (push + reducer warps)
@@ -252,6 +253,7 @@ __device__ __forceinline__ bool gemm_epilogue_tile(const GemmParams& p, Hooks& h
                   dst.ll_off + 8ull * ((unsigned long long)(drow - dst.ll_row0) * (dst.ll_ld ? dst.ll_ld : dst.ld) +
                                        (unsigned long long)(dcol - dst.ll_col0));
               const unsigned long long v = ((unsigned long long)dst.ll_tag << 32) | r[j];
+              if (!kr_in_bounds(o >= p.ll_off && o + 8 <= p.ll_end, p.sync, 76)) continue;
               if (dst.ll_dst >= 0) {
                 st_relaxed_sys_u64((char*)p.peer_buf[dst.ll_dst] + o, v);
               } else {

@@ -75,6 +75,10 @@ struct ArHooksT : HookDefaults {
   // Polls `nsl` slots (stride `stride` bytes) of four consecutive tagged pairs at `src` until all
   // carry the tag and adds the values, slot after slot, into acc. False when the wait gave up.
   __device__ __forceinline__ bool poll_quad(const GemmParams& p, const char* src, size_t stride, int nsl, float (&acc)[4]) {
+    {
+      const size_t first = (size_t)(src - (const char*)p.peer_buf[p.rank]);
+      if (!kr_in_bounds(first >= p.ll_off && first + (size_t)(nsl - 1) * stride + 32 <= p.ll_end, p.sync, 77)) return false;
+    }
     for (int s0 = 0; s0 < nsl; s0 += 4) {
       unsigned long long v[4][4];
       const bool ok = spin_until(
