@@ -142,3 +142,20 @@ def _gloo_rank_skips(rank, ws):
 
 def test_gloo_missing_rank_times_out():
     run_distributed(_gloo_rank_skips, 2, "gloo")
+
+
+def test_config_sizing_overrides(monkeypatch):
+    from kraken_b200 import config
+    from kraken_b200.comm.all_reduce import push_limit_bytes
+
+    assert config.push_tagged_max_bytes() == 64 << 10
+    monkeypatch.setenv("KRAKEN_PUSH_TAGGED_KB", "0")
+    assert config.push_tagged_max_bytes() == 0
+    assert config.gemm_flops_per_s() == 1450e12
+    monkeypatch.setenv("KRAKEN_GEMM_TFLOPS", "1000")
+    assert config.gemm_flops_per_s() == 1000e12
+    assert config.comm_cta_bytes_per_s("pull") == 15e9 and config.comm_cta_bytes_per_s("multicast") == 10e9
+    monkeypatch.setenv("KRAKEN_COMM_CTA_GBS_PUSH", "33")
+    assert config.comm_cta_bytes_per_s("push") == 33e9
+    # push-style one-shot: the limit shrinks with the world size and stops where pulling was measured faster
+    assert push_limit_bytes(2) == 2 << 20 and push_limit_bytes(8) == 1 << 20 and push_limit_bytes(4) == 1 << 20
