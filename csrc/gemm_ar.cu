@@ -78,12 +78,14 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
   };
   auto t_main = [&](int ks) { const double a1 = cta_bytes / ks / 80e9, a2 = all_bytes / 6.5e12; return a1 > a2 ? a1 : a2; };
   auto t_xfer = [&](int al, int ks) {
-    // fixed costs as measured on top of the plain GEMM of the same shape: flag round trips of the
-    // one- and two-shot forms against none for the tagged push
-    if (al == 3) return 3e-6 + (double)(ks + 1) * (ws - 1) / ws * mn * 8 / 400e9;
-    if (al == 2) return 1e-6 + (double)ks * (ws - 1) * mn * 8 / 400e9;
-    if (al == 1) return 11e-6 + (double)(ks + 1) * (ws - 1) / ws * mn4 / 600e9;
-    return 9e-6 + (double)(ws - 1) * mn4 / 400e9;
+    // Fixed costs as measured on top of the plain GEMM of the same shape at 2 and 8 ranks (they grow
+    // with the number of peers: flag round trips for the one- and two-shot forms, polling for the
+    // tagged ones), plus the bytes a rank receives at the rate each form was seen to reach.
+    const double peers = (double)(ws - 1);
+    if (al == 3) return (3.0 + 1.3 * peers) * 1e-6 + (double)(ks + 1) * peers / ws * mn * 8 / 400e9;
+    if (al == 2) return (1.0 + 1.1 * peers) * 1e-6 + (double)ks * peers * mn * 8 / 400e9;
+    if (al == 1) return (11.0 + 1.2 * peers) * 1e-6 + (double)(ks + 1) * peers / ws * mn4 / 600e9;
+    return (9.0 + 0.15 * peers) * 1e-6 + peers * mn4 / 400e9;
   };
   pl.algo = -1;
   pl.ks = 1;
@@ -95,9 +97,6 @@ static bool ar_plan(const DeviceState* d, int M, int N, int K, int ws, int swap_
     // at 2 ranks both move the same bytes and one-shot has one flag hop less (measured faster at every M)
     if (algo < 0 && al == 0 && ws > 2 && (unsigned long long)(ws - 1) * mn4 > (1ull << 20)) continue;
     if (algo < 0 && al == 1 && ws == 2 && mn4 <= S / 8) continue;
-    // the tagged two-shot is chosen on request only: its place in the cost model has not been
-    // calibrated at 4 and 8 ranks, where it is meant to replace the flag two-shot for decode rows
-    if (algo < 0 && al == 3) continue;
     for (int ks = 1; ks <= 4; ++ks) {
       if (k_splits > 0 && ks != k_splits) continue;
       if (!ks_ok(ks)) continue;
