@@ -60,7 +60,7 @@ def push_workspace(group, device):
 def _push_all_reduce(inp: torch.Tensor, bias, out: torch.Tensor, group) -> None:
     hdl, pads, seq = push_workspace(group, inp.device)
     bias_ptr, bias_n = _bias_args(bias, inp)
-    tagged = config.push_tagged_max_bytes()
+    tagged = config.push_tagged_max_bytes(hdl.world_size)
     _dump(f"one_shot_all_reduce push numel={inp.numel()} ws={hdl.world_size} nvls={bool(hdl.multicast_ptr)} "
           f"tagged={inp.numel() * 2 <= tagged}")
     _lib.check(_lib.lib().kr_push_all_reduce(

@@ -91,7 +91,7 @@ def _ar_bias_rms_norm(symm_buf, x, bias, w, y, eps, group, algo: int, one_shot: 
         _dump(f"one_shot_all_reduce_bias_rms_norm push rows={rows} D={D} ws={ph.world_size} nvls={bool(ph.multicast_ptr)}")
         _lib.check(_lib.lib().kr_push_all_reduce_bias_rms_norm(
             ph._host_ptr_array, pads, ph.multicast_ptr or None, ph.rank, ph.world_size, x.data_ptr(), bias_ptr, bias_n,
-            w.data_ptr(), y.data_ptr(), rows, D, float(eps), seq, config.push_tagged_max_bytes(), ph.buffer_size, 0,
+            w.data_ptr(), y.data_ptr(), rows, D, float(eps), seq, config.push_tagged_max_bytes(ph.world_size), ph.buffer_size, 0,
             _lib.current_stream_ptr()))
         return
     mc = None

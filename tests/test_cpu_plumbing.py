@@ -148,7 +148,7 @@ def test_config_sizing_overrides(monkeypatch):
     from kraken_b200 import config
     from kraken_b200.comm.all_reduce import push_limit_bytes
 
-    assert config.push_tagged_max_bytes() == 64 << 10
+    assert config.push_tagged_max_bytes() == 64 << 10 and config.push_tagged_max_bytes(2) == 512 << 10
     monkeypatch.setenv("KRAKEN_PUSH_TAGGED_KB", "0")
     assert config.push_tagged_max_bytes() == 0
     assert config.gemm_flops_per_s() == 1450e12
